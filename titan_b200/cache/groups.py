@@ -13,6 +13,8 @@ storage, pages and a block table of its own:
 * ``KVGroup`` with ``window=n`` keeps a ring of the last ``ring_rows`` rows
   (``n`` rounded up to whole pages): position ``p`` lives in ring row
   ``p % ring_rows``;
+* ``LatentGroup`` is a KVGroup with one plane: one row per token that serves as
+  key and as value (latent attention);
 * ``StateGroup`` keeps a tensor of fixed size per sequence and layer (no time
   axis), zeroed when a slot is handed out.
 
@@ -115,6 +117,8 @@ STALE_MARK = 3.0e4        # what a freed page holds when the cache is asked to m
 
 
 class KVGroup(CacheGroup):
+    planes = 2                 # K and V; a group that keeps one row per token (LatentGroup) has one
+
     def __init__(self, need: CacheNeed, layers: List[int], geometry: CacheGeometry):
         self.need, self.layers = need, list(layers)
         page_size, num_pages, device = geometry.page_size, geometry.num_pages, geometry.device
@@ -132,7 +136,7 @@ class KVGroup(CacheGroup):
         self.pages_of: Dict[int, List[int]] = {}
         # zeroed once: rows past a sequence's end are multiplied by a zero weight in the tensor-core
         # kernels, so they must hold finite numbers (a freed page keeps its old, finite, rows)
-        self.storage = torch.zeros((len(layers), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
+        self.storage = torch.zeros((len(layers), self.planes, num_pages, need.num_kv_heads, page_size, need.head_dim),
                                    dtype=geometry.dtype, device=device)
         self.table = torch.zeros((geometry.max_slots, self.table_width), dtype=torch.int32, device=device)
         self._pin = torch.device(device).type == "cuda"
@@ -214,5 +218,13 @@ class StateGroup(CacheGroup):
         return self.storage.numel() * self.storage.element_size()
 
 
+class LatentGroup(KVGroup):
+    """One row per token and layer instead of a key and a value per head: the compressed latent and the rotated key part
+    that every head of a latent-attention mixer shares (``head_dim`` = the row's width, ``num_kv_heads`` = 1).  Pages,
+    block table and the ring of a window are KVGroup's; the storage is [layers, 1, pages, 1, page_size, width]."""
+    planes = 1
+
+
+register_cache_group("latent", LatentGroup)
 register_cache_group("kv", KVGroup)
 register_cache_group("state", StateGroup)

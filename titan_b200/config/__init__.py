@@ -1,10 +1,12 @@
 from .spec import (ConfigError, FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
                    PositionSpec)
 from .qwen3 import Qwen3Config
+from .tefezen import TefezenConfig
 from .registry import config_from_dict, known_architectures, load_config, register_architecture
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config)
+register_architecture("Tefezen", TefezenConfig)
 
 __all__ = ["ConfigError", "FeedForwardSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec",
-           "PositionSpec", "Qwen3Config", "config_from_dict", "known_architectures", "load_config",
+           "PositionSpec", "Qwen3Config", "TefezenConfig", "config_from_dict", "known_architectures", "load_config",
            "register_architecture"]

@@ -1,4 +1,4 @@
-"""The one registry from an architecture's name (config.json ``architectures[0]``)
+"""The one registry from an architecture's name (config.json ``architectures[0]``, or ``architecture``)
 to its typed configuration and its model.
 
 berniehans/titan has no registry: ``ForwardDriver`` serves the dense family and
@@ -35,6 +35,8 @@ def known_architectures():
 
 def config_from_dict(d: Dict[str, Any]):
     archs = d.get("architectures")
+    if isinstance(d.get("architecture"), str) and not archs:        # some descriptions name it once, as a string
+        archs = [d["architecture"]]
     if not archs or not isinstance(archs, list):
         raise ConfigError("config.json lacks the key 'architectures'")
     name = archs[0]

@@ -27,6 +27,7 @@ class NormSpec:
     size: int
     eps: float
     weight: str               # tensor name relative to the owner's prefix
+    weight_offset: float = 0.0  # the rows are multiplied by (weight_offset + stored weight): 1.0 for weights stored around zero
 
 
 @dataclass(frozen=True)
@@ -34,7 +35,7 @@ class PositionSpec:
     kind: str                 # "rope" | "none"
     rotary_dim: int = 0       # leading dims of a head that are rotated
     theta: float = 10000.0
-    pairing: str = "half"     # (k, k + rotary_dim/2)
+    pairing: str = "half"     # "half": (k, k + rotary_dim/2) turn together; "adjacent": (2k, 2k + 1)
 
 
 def _lookup(pairs, key, default):
@@ -46,7 +47,7 @@ def _lookup(pairs, key, default):
 
 @dataclass(frozen=True)
 class MixerSpec:
-    kind: str                 # "attention"
+    kind: str                 # "attention" | "latent_attention" | "lightning"
     hidden_size: int
     num_heads: int = 0
     num_kv_heads: int = 0
@@ -72,7 +73,7 @@ class MixerSpec:
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str                 # "gated_mlp"
+    kind: str                 # "gated_mlp" | "moe" | "token_table"
     hidden_size: int
     intermediate_size: int = 0
     activation: str = "silu"
@@ -96,7 +97,7 @@ class LayerSpec:
     feed-forward (None), or take more norms than two from ``norms`` (a norm after each part as well as
     before it, say) and its own constants from ``extra``."""
     index: int
-    arrangement: str          # "pre_norm"
+    arrangement: str          # "pre_norm" | "output_norm"
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
     mixer_norm: Optional[NormSpec]
@@ -123,6 +124,9 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     embedding_scale: Optional[float] = None   # the embedded rows are multiplied by this (None: as stored)
     logit_scale: Optional[float] = None       # the logits are multiplied by this (None: as computed)
+    # Tensors that no single layer owns (a table that every layer reads a slice of): (name, shape) pairs.  The model
+    # loads each once and hands the dict to every part that has ``bind_shared``.
+    shared_tensors: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
     def validate(self) -> None:
         if not self.layers:
@@ -144,11 +148,36 @@ class ModelSpec:
             owner = self.layers[src].mixer
             if owner.kind != me.kind:
                 raise ConfigError(f"layer {layer.index} ({me.kind}) reads the cache of layer {src}, whose mixer is of another kind ({owner.kind})")
-            if owner.window != me.window:
-                raise ConfigError(f"layer {layer.index} reads the cache of layer {src}, which keeps a window of {owner.window} keys, "
-                                  f"with a window of {me.window}: a reader must see exactly what the owner keeps")
-            if owner.head_dim != me.head_dim:
-                raise ConfigError(f"layer {layer.index} has heads of {me.head_dim}, the cache of layer {src} holds heads of {owner.head_dim}")
-            if owner.num_kv_heads <= 0 or me.num_heads % owner.num_kv_heads:
-                raise ConfigError(f"layer {layer.index} has {me.num_heads} query heads, not a multiple of the {owner.num_kv_heads} "
-                                  f"kv heads in the cache of layer {src}")
+            why = _SHARING_RULES.get(me.kind, lambda *a: None)(layer.index, me, src, owner)
+            if why:
+                raise ConfigError(why)
+
+
+def _share_kv(index, me, src, owner):
+    """Grouped-query attention reading another layer's keys and values."""
+    if owner.window != me.window:
+        return (f"layer {index} reads the cache of layer {src}, which keeps a window of {owner.window} keys, "
+                f"with a window of {me.window}: a reader must see exactly what the owner keeps")
+    if owner.head_dim != me.head_dim:
+        return f"layer {index} has heads of {me.head_dim}, the cache of layer {src} holds heads of {owner.head_dim}"
+    if owner.num_kv_heads <= 0 or me.num_heads % owner.num_kv_heads:
+        return (f"layer {index} has {me.num_heads} query heads, not a multiple of the {owner.num_kv_heads} "
+                f"kv heads in the cache of layer {src}")
+    return None
+
+
+def _share_latent(index, me, src, owner):
+    """Latent attention reading another layer's latents: the cached row must mean the same to both (latent size,
+    rotated size, rotation), and the owner must keep at least the keys the reader's window reaches."""
+    for key in ("kv_rank", "rot_dim"):
+        if owner.option(key) != me.option(key):
+            return f"layer {index} has {key} {me.option(key)}, the cache of layer {src} holds {key} {owner.option(key)}"
+    if owner.position != me.position:
+        return f"layer {index} rotates its keys otherwise than layer {src}, whose cache it reads"
+    kept = owner.option("cache_window", owner.window)
+    if kept is not None and (me.window is None or me.window > kept):
+        return f"layer {index} looks {me.window} keys back, the cache of layer {src} keeps {kept}"
+    return None
+
+
+_SHARING_RULES = {"attention": _share_kv, "latent_attention": _share_latent}

@@ -21,7 +21,8 @@
 #include "attention_args.h"
 #include "common.cuh"
 
-#define ATT_MAXE 8        // head_dim <= 256
+#define ATT_MAXE 8        // head_dim <= 256 (the wide instantiation: 32 values a lane, rows up to 1,024)
+#define ATT_MAXE_WIDE 32
 #define ATT_WARPS 4
 
 
@@ -41,20 +42,25 @@ template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bflo
 }
 
 // Running softmax state of one warp: every lane holds the same m and l, and acc for dims lane + 32 j.
+template <int MAXE>
 struct Running {
     float m, l;
-    float acc[ATT_MAXE];
+    float acc[MAXE];
 };
+
+// Width of a value row (and of an output row): the key's width unless the launch says otherwise.
+__device__ __host__ __forceinline__ int value_width(const AttnArgs& a) { return a.hd_v > 0 ? a.hd_v : a.hd; }
 
 // Folds keys [lo, hi) of one sequence into ``st``.  Keys at positions >= first_new are read from the
 // step's own rows (row index first_new_row + pos - first_new), earlier ones from the cache.
-template <typename T>
-__device__ __forceinline__ void attend_range(Running& st, const float* qs, const AttnArgs& a, int lo, int hi,
+template <typename T, int MAXE>
+__device__ __forceinline__ void attend_range(Running<MAXE>& st, const float* qs, const AttnArgs& a, int lo, int hi,
                                              int first_new, int first_new_row, int slot, int kh, int lane) {
-    const int hd = a.hd;
+    const int hd = a.hd, hdv = value_width(a);
     const T* knew = (const T*)a.kv_new;
     const T* cache = (const T*)a.cache.storage;
-    const size_t vhalf = cache ? kv_half_elems(a.cache) : 0;
+    const size_t vhalf = (cache && !a.v_alias) ? kv_half_elems(a.cache) : 0;
+    const int vnew = a.v_alias ? 0 : a.nkv * hd;
     for (int base = lo; base < hi; base += 32) {
         const int kpos = base + lane;
         const bool valid = kpos < hi;
@@ -63,7 +69,7 @@ __device__ __forceinline__ void attend_range(Running& st, const float* qs, const
         if (valid) {
             if (kpos >= first_new) {
                 kp = knew + (size_t)(first_new_row + kpos - first_new) * a.kv_stride + kh * hd;
-                vp = kp + a.nkv * hd;
+                vp = kp + vnew;
             } else {
                 kp = cache + kv_row_offset(a.cache, slot, kpos, kh);
                 vp = kp + vhalf;
@@ -86,15 +92,15 @@ __device__ __forceinline__ void attend_range(Running& st, const float* qs, const
         st.l = st.l * alpha + warp_sum(p);
         st.m = m_new;
 #pragma unroll
-        for (int j = 0; j < ATT_MAXE; ++j) st.acc[j] *= alpha;
+        for (int j = 0; j < MAXE; ++j) st.acc[j] *= alpha;
         const int n_valid = min(32, hi - base);
         for (int kk = 0; kk < n_valid; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, p, kk);
             const T* v = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)vp, kk);
 #pragma unroll
-            for (int j = 0; j < ATT_MAXE; ++j) {
+            for (int j = 0; j < MAXE; ++j) {
                 const int d = lane + 32 * j;
-                if (d < hd) st.acc[j] = fmaf(pk, ldf(v + d), st.acc[j]);
+                if (d < hdv) st.acc[j] = fmaf(pk, ldf(v + d), st.acc[j]);
             }
         }
     }
@@ -108,7 +114,7 @@ __device__ __forceinline__ void load_query(float* qs, const T* q, int hd, int la
 
 // ------------------------------------------------------------------ prefill
 // grid (T, ceil(nh / ATT_WARPS)); warp = one head of one query token.
-template <typename T>
+template <typename T, int MAXE>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -123,17 +129,18 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a
     const int slot = a.batch.slot_of_seq[seq];
     const int first_new = a.kv_new ? a.batch.start_pos[seq] : 0x7fffffff;
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    Running st;
+    Running<MAXE> st;
     st.m = -FLT_MAX; st.l = 0.f;
 #pragma unroll
-    for (int j = 0; j < ATT_MAXE; ++j) st.acc[j] = 0.f;
-    attend_range<T>(st, qs, a, lo, pos + 1, first_new, a.batch.q_start[seq], slot, h / (a.nh / a.nkv), lane);
+    for (int j = 0; j < MAXE; ++j) st.acc[j] = 0.f;
+    attend_range<T, MAXE>(st, qs, a, lo, pos + 1, first_new, a.batch.q_start[seq], slot, h / (a.nh / a.nkv), lane);
     const float inv = 1.0f / st.l;
-    T* o = (T*)a.out + (size_t)t * a.out_stride + h * hd;
+    const int hdv = value_width(a);
+    T* o = (T*)a.out + (size_t)t * a.out_stride + h * hdv;
 #pragma unroll
-    for (int j = 0; j < ATT_MAXE; ++j) {
+    for (int j = 0; j < MAXE; ++j) {
         const int d = lane + 32 * j;
-        if (d < hd) stf(o + d, st.acc[j] * inv);
+        if (d < hdv) stf(o + d, st.acc[j] * inv);
     }
 }
 
@@ -141,14 +148,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a
 // grid (B, nkv, n_splits); the warps of a block take the query heads of one kv head in turn.
 // Partial of (sequence b, head h, split s) at scratch[((b * nh + h) * n_splits + s) * (hd + 2)]:
 // hd unnormalised outputs, then m, then l (l = 0: the split saw no key).
-template <typename T>
+template <typename T, int MAXE>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float q_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
-    const int hd = a.hd, group = a.nh / a.nkv;
+    const int hd = a.hd, hdv = value_width(a), group = a.nh / a.nkv;
     const int len = a.batch.kv_len[b];
     const int keys = tb_split_keys(len, a.chunk, a.n_splits);
     if ((long long)split * keys >= len) return;     // the merge reads ceil(len / keys) splits only
@@ -159,33 +166,33 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     float* qs = q_smem + warp * hd;
     for (int g = warp; g < group; g += ATT_WARPS) {
         const int h = kh * group + g;
-        float* part = a.scratch + ((size_t)(b * a.nh + h) * a.n_splits + split) * (hd + 2);
-        Running st;
+        float* part = a.scratch + ((size_t)(b * a.nh + h) * a.n_splits + split) * (hdv + 2);
+        Running<MAXE> st;
         st.m = -FLT_MAX; st.l = 0.f;
 #pragma unroll
-        for (int j = 0; j < ATT_MAXE; ++j) st.acc[j] = 0.f;
+        for (int j = 0; j < MAXE; ++j) st.acc[j] = 0.f;
         if (lo < hi) {
             __syncwarp();
             load_query<T>(qs, (const T*)a.q + (size_t)b * a.q_stride + h * hd, hd, lane);
-            attend_range<T>(st, qs, a, lo, hi, 0x7fffffff, 0, slot, kh, lane);
+            attend_range<T, MAXE>(st, qs, a, lo, hi, 0x7fffffff, 0, slot, kh, lane);
         }
 #pragma unroll
-        for (int j = 0; j < ATT_MAXE; ++j) {
+        for (int j = 0; j < MAXE; ++j) {
             const int d = lane + 32 * j;
-            if (d < hd) part[d] = st.acc[j];
+            if (d < hdv) part[d] = st.acc[j];
         }
-        if (lane == 0) { part[hd] = st.m; part[hd + 1] = st.l; }
+        if (lane == 0) { part[hdv] = st.m; part[hdv + 1] = st.l; }
     }
 }
 
 // grid (B, nh), one warp: out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits in order.
 // Lane s holds the weight of split s (32 splits per round), so the loads of the accumulation are
 // independent of one another.
-template <typename T>
+template <typename T, int MAXE>
 __global__ void attn_merge_kernel(AttnArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = a.hd, stride = hd + 2;
+    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = value_width(a), stride = hd + 2;
     const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
     const int len = a.batch.kv_len[b], keys = tb_split_keys(len, a.chunk, a.n_splits);
     const int used = min(a.n_splits, (len + keys - 1) / keys);
@@ -193,9 +200,9 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     for (int s = lane; s < used; s += 32)
         if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
     m = warp_max(m);
-    float l = 0.f, acc[ATT_MAXE];
+    float l = 0.f, acc[MAXE];
 #pragma unroll
-    for (int j = 0; j < ATT_MAXE; ++j) acc[j] = 0.f;
+    for (int j = 0; j < MAXE; ++j) acc[j] = 0.f;
     for (int s0 = 0; s0 < used; s0 += 32) {
         const int s = s0 + lane;
         float w = 0.f;
@@ -208,7 +215,7 @@ __global__ void attn_merge_kernel(AttnArgs a) {
             const float wk = __shfl_sync(0xffffffffu, w, k);
             const float* p = part + (size_t)(s0 + k) * stride;
 #pragma unroll
-            for (int j = 0; j < ATT_MAXE; ++j) {
+            for (int j = 0; j < MAXE; ++j) {
                 const int d = lane + 32 * j;
                 if (d < hd) acc[j] = fmaf(wk, p[d], acc[j]);
             }
@@ -218,7 +225,7 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     const float inv = 1.0f / l;
     T* o = (T*)a.out + (size_t)b * a.out_stride + h * hd;
 #pragma unroll
-    for (int j = 0; j < ATT_MAXE; ++j) {
+    for (int j = 0; j < MAXE; ++j) {
         const int d = lane + 32 * j;
         if (d < hd) stf(o + d, acc[j] * inv);
     }
@@ -226,33 +233,49 @@ __global__ void attn_merge_kernel(AttnArgs a) {
 
 static int check_common(const AttnArgs& a, const char* who) {
     TB_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "%s: %d query heads are not a multiple of %d kv heads", who, a.nh, a.nkv);
-    TB_REQUIRE(a.hd >= 8 && a.hd % 8 == 0 && a.hd <= 32 * ATT_MAXE, "%s: head_dim %d must be a multiple of 8 up to %d", who, a.hd, 32 * ATT_MAXE);
+    TB_REQUIRE(a.hd >= 8 && a.hd % 8 == 0 && a.hd <= 32 * ATT_MAXE_WIDE, "%s: head_dim %d must be a multiple of 8 up to %d", who, a.hd, 32 * ATT_MAXE_WIDE);
+    TB_REQUIRE(a.hd_v >= 0 && a.hd_v <= 32 * ATT_MAXE_WIDE, "%s: a value row of %d elements (at most %d)", who, a.hd_v, 32 * ATT_MAXE_WIDE);
+    TB_REQUIRE(!a.v_alias || value_width(a) <= a.hd, "%s: a value that is the head of its key row cannot be wider (%d) than the key (%d)", who, value_width(a), a.hd);
     TB_REQUIRE(a.q_stride % 8 == 0 && a.kv_stride % 8 == 0, "%s: row strides must be multiples of 8 elements", who);
     TB_REQUIRE(a.window >= 0, "%s: negative window", who);
     TB_REQUIRE(!a.cache.storage || (a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv), "%s: the cache view does not match the heads", who);
     return 0;
 }
 
+// Rows of up to 256 elements take 8 values a lane, wider ones 32.
+static bool wide_rows(const AttnArgs& a) { return a.hd > 32 * ATT_MAXE || value_width(a) > 32 * ATT_MAXE; }
+
+#define ATT_DISPATCH(kernel, grid, threads, smem)                                                              \
+    do {                                                                                                       \
+        if (dtype == TB_F32) {                                                                                 \
+            if (wide) tb_launch(kernel<float, ATT_MAXE_WIDE>, grid, threads, smem, stream, a);                 \
+            else tb_launch(kernel<float, ATT_MAXE>, grid, threads, smem, stream, a);                           \
+        } else {                                                                                               \
+            if (wide) tb_launch(kernel<__nv_bfloat16, ATT_MAXE_WIDE>, grid, threads, smem, stream, a);         \
+            else tb_launch(kernel<__nv_bfloat16, ATT_MAXE>, grid, threads, smem, stream, a);                   \
+        }                                                                                                      \
+    } while (0)
+
 extern "C" int tb_attn_prefill(const AttnArgs* args, int dtype, cudaStream_t stream) {
     AttnArgs a = *args;
     if (check_common(a, "attn_prefill")) return 1;
+    TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_prefill: unknown dtype %d", dtype);
     TB_REQUIRE(a.batch.T > 0, "attn_prefill: no tokens");
     TB_REQUIRE(a.kv_new || a.cache.storage, "attn_prefill: neither new keys nor a cache");
     dim3 grid(a.batch.T, (a.nh + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
-    if (dtype == TB_F32) tb_launch(attn_prefill_kernel<float>, grid, ATT_WARPS * 32, smem, stream, a);
-    else if (dtype == TB_BF16) tb_launch(attn_prefill_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream, a);
-    else TB_REQUIRE(false, "attn_prefill: unknown dtype %d", dtype);
+    const bool wide = wide_rows(a);
+    ATT_DISPATCH(attn_prefill_kernel, grid, ATT_WARPS * 32, smem);
     TB_CHECK_LAUNCH("attn_prefill");
     return 0;
 }
 
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream) {
     AttnArgs a = *args;
+    TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_merge: unknown dtype %d", dtype);
     dim3 mgrid(a.batch.B, a.nh);
-    if (dtype == TB_F32) tb_launch(attn_merge_kernel<float>, mgrid, 32, 0, stream, a);
-    else if (dtype == TB_BF16) tb_launch(attn_merge_kernel<__nv_bfloat16>, mgrid, 32, 0, stream, a);
-    else TB_REQUIRE(false, "attn_merge: unknown dtype %d", dtype);
+    const bool wide = wide_rows(a);
+    ATT_DISPATCH(attn_merge_kernel, mgrid, 32, 0);
     TB_CHECK_LAUNCH("attn_merge");
     return 0;
 }
@@ -260,18 +283,15 @@ extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t strea
 extern "C" int tb_attn_decode(const AttnArgs* args, int dtype, cudaStream_t stream) {
     AttnArgs a = *args;
     if (check_common(a, "attn_decode")) return 1;
+    TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_decode: unknown dtype %d", dtype);
     TB_REQUIRE(a.batch.B > 0 && a.cache.storage && a.scratch, "attn_decode: needs sequences, a cache and scratch");
     TB_REQUIRE(a.chunk > 0 && a.n_splits > 0 && a.n_splits <= 65535, "attn_decode: bad split (chunk=%d splits=%d)", a.chunk, a.n_splits);
     TB_REQUIRE(a.nkv <= 65535, "attn_decode: too many kv heads");
     dim3 grid(a.batch.B, a.nkv, a.n_splits), mgrid(a.batch.B, a.nh);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
-    if (dtype == TB_F32) {
-        tb_launch(attn_decode_kernel<float>, grid, ATT_WARPS * 32, smem, stream, a);
-        tb_launch(attn_merge_kernel<float>, mgrid, 32, 0, stream, a);
-    } else if (dtype == TB_BF16) {
-        tb_launch(attn_decode_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream, a);
-        tb_launch(attn_merge_kernel<__nv_bfloat16>, mgrid, 32, 0, stream, a);
-    } else TB_REQUIRE(false, "attn_decode: unknown dtype %d", dtype);
+    const bool wide = wide_rows(a);
+    ATT_DISPATCH(attn_decode_kernel, grid, ATT_WARPS * 32, smem);
+    ATT_DISPATCH(attn_merge_kernel, mgrid, 32, 0);
     TB_CHECK_LAUNCH("attn_decode");
     return 0;
 }

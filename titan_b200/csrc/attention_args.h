@@ -30,6 +30,11 @@ struct AttnArgs {
     // fused_qk->in_stride: Q heads, K heads, V heads), with the norm weights, the rotary block, the row scales and the
     // cache of *fused_qk; ``q`` is not read.  Null: queries are bfloat16 rows at ``q`` and the cache holds every key.
     const QkArgs* fused_qk;
+    // Keys and values of unequal width (the any-size kernels only; zero: both are ``hd`` wide).  hd_v: width of a
+    // value row, of a head's output row and of the scratch partials.  v_alias: a value row is the first hd_v
+    // elements of its key row (one stored row per token serves as both: attention in a shared latent space, where
+    // the key is [latent | rotated part] and the value the latent alone), so no V plane or V columns are read.
+    int hd_v; int v_alias;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

@@ -729,6 +729,7 @@ extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 :
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
     TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
+    TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
     TB_REQUIRE(a->cache.page_size == PAGE, "attn_decode_mma: pages of %d rows, not %d", PAGE, a->cache.page_size);
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0 && a->nh / a->nkv <= 16, "attn_decode_mma: at most 16 query heads per kv head");
     TB_REQUIRE(a->chunk > 0 && a->chunk % PAGE == 0, "attn_decode_mma: the chunk %d must be a multiple of %d", a->chunk, PAGE);
@@ -737,6 +738,7 @@ extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
         TB_REQUIRE(q.in && q.in_stride % 4 == 0 && ((uintptr_t)q.in & 15) == 0, "attn_decode_mma: the projection's sums must be 16-byte aligned float32 rows");
         TB_REQUIRE(q.nh == a->nh && q.nkv == a->nkv && q.hd == a->hd, "attn_decode_mma: the folded head norm's heads do not match");
         TB_REQUIRE(!q.rope.inv_freq || q.rope.rot == a->hd, "attn_decode_mma: the folded rotation must span the whole head");
+        TB_REQUIRE(!q.rope.adjacent, "attn_decode_mma: the folded rotation pairs dimension k with k + rot/2 only");
         TB_REQUIRE(q.cache.storage == a->cache.storage, "attn_decode_mma: the folded append writes the cache it reads");
         TB_REQUIRE(!q.row_sumsq || (q.row_width > 0 && q.row_parts > 0 && q.row_parts <= 16 && a->batch.B <= 32), "attn_decode_mma: row sums of squares need their width, 1 to 16 parts and at most 32 rows");
         const bool wide = a->nh / a->nkv > 8;
@@ -818,6 +820,7 @@ extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int sourc
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
+    TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0, "attn_prefill_mma: heads");
     TB_REQUIRE(a->q_stride % 8 == 0 && ((uintptr_t)a->q & 15) == 0, "attn_prefill_mma: the queries must be 16-byte aligned rows");
     if (source == TB_KV_FROM_STEP) {

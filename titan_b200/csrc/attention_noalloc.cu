@@ -42,7 +42,7 @@ extern "C" int tb_attn_decode_noalloc(const AttnArgs* args, int dtype, cudaStrea
     TB_REQUIRE(args, "attn_decode_noalloc: no arguments");
     AttnArgs a = *args;
     TB_REQUIRE(a.batch.B > 0 && a.nh > 0 && a.n_splits > 0 && a.hd > 0, "attn_decode_noalloc: sizes must be positive");
-    const unsigned long long need = (unsigned long long)a.batch.B * a.nh * a.n_splits * (a.hd + 2);
+    const unsigned long long need = (unsigned long long)a.batch.B * a.nh * a.n_splits * ((a.hd_v > 0 ? a.hd_v : a.hd) + 2);
     TB_REQUIRE(need <= TB_NOALLOC_SCRATCH_FLOATS,
                "attn_decode_noalloc: %d sequences x %d heads x %d splits x (%d + 2) need %llu scratch values; the built-in "
                "scratch holds %u (use tb_attn_decode with a buffer of your own, or fewer splits)",

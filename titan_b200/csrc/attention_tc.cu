@@ -366,6 +366,7 @@ extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == HD, "attn_prefill_tc: head_dim %d is not %d", a->hd, HD);
+    TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0, "attn_prefill_tc: heads");
     TB_REQUIRE(a->q_stride % 8 == 0 && ((uintptr_t)a->q & 15) == 0, "attn_prefill_tc: the queries must be 16-byte aligned rows");
     if (source == TB_KV_FROM_STEP) {

@@ -432,6 +432,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
     TB_REQUIRE(a.hd > 0 && a.hd <= 32 * QK_MAXE, "qk_norm_rope: head_dim %d is not in 1..%d", a.hd, 32 * QK_MAXE);
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot <= a.hd && a.rope.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rope.rot, a.hd);
+    TB_REQUIRE(!a.rope.adjacent, "qk_norm_rope: this kernel pairs dimension k with k + rot/2 only");
     TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
                "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
     TB_REQUIRE(!a.row_sumsq || (a.row_width > 0 && a.row_parts > 0 && a.T <= 32), "qk_norm_rope: row sums of squares need the rows' width, their number of parts and at most 32 rows");
@@ -547,5 +548,91 @@ extern "C" int tb_commit_lengths(const int* slot_of_seq, const int* kv_len, int*
     TB_REQUIRE(B > 0, "commit_lengths: no sequences");
     tb_launch(commit_lengths_kernel, (B + 127) / 128, 128, 0, stream, slot_of_seq, kv_len, seq_len, B);
     TB_CHECK_LAUNCH("commit_lengths");
+    return 0;
+}
+
+// ------------------------------------------------------------------ norm on a sublayer's OUTPUT, added to the residual
+// x[r] += y[r] / sqrt(mean(y[r]^2) + eps) * w, all float32, for blocks whose norms follow their sublayers.
+// Fused with it: ``y`` may be left zeroed (it is the buffer the next sublayer's products add into), and the new
+// residual row may also be written rounded to the compute dtype (``lowp``), which is what the next sublayer's
+// first product reads.  One block per row; the row is read twice (second time from L1/L2).
+template <typename T>
+__global__ void rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x,
+                                   T* __restrict__ lowp, int H, float eps, int zero_y) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    float* yr = y + r * H;
+    float* xr = x + r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * scale * w[i];
+        xr[i] = v;
+        if (lowp) stf(lowp + r * H + i, v);
+        if (zero_y) yr[i] = 0.f;
+    }
+}
+
+extern "C" int tb_rmsnorm_add(float* y, const float* w, float* x, void* lowp, int lowp_dtype, int n_rows, int H,
+                              float eps, int zero_y, cudaStream_t stream) {
+    TB_REQUIRE(n_rows > 0 && H > 0 && y && w && x, "rmsnorm_add: sizes must be positive (rows=%d H=%d)", n_rows, H);
+    const int threads = H >= 2048 ? 256 : (H >= 512 ? 128 : 64);
+    if (!lowp || lowp_dtype == TB_F32) tb_launch(rmsnorm_add_kernel<float>, n_rows, threads, 0, stream, y, w, x, (float*)lowp, H, eps, zero_y);
+    else if (lowp_dtype == TB_BF16) tb_launch(rmsnorm_add_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, y, w, x, (__nv_bfloat16*)lowp, H, eps, zero_y);
+    else TB_REQUIRE(false, "rmsnorm_add: unknown dtype %d", lowp_dtype);
+    TB_CHECK_LAUNCH("rmsnorm_add");
+    return 0;
+}
+
+// out[i] = x[i] rounded to bfloat16: the residual stream as the first product of a sublayer reads it, where no
+// kernel before has left that copy.
+__global__ void round_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = __float2bfloat16_rn(x[i]);
+}
+
+extern "C" int tb_round_rows(const float* x, void* out, long long n, cudaStream_t stream) {
+    TB_REQUIRE(x && out && n > 0, "round_rows: nothing to round");
+    const long long blocks = (n + 255) / 256;
+    tb_launch(round_rows_kernel, (int)(blocks < 8192 ? blocks : 8192), 256, 0, stream, x, (__nv_bfloat16*)out, n);
+    TB_CHECK_LAUNCH("round_rows");
+    return 0;
+}
+
+// ------------------------------------------------------------------ gate of a per-token table input
+// g[t][d] = act(z[t][d]) * table[token[t]][offset + d], act = gelu in its tanh form:
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), float32 inside.
+template <typename T>
+__global__ void gelu_mul_table_kernel(const T* __restrict__ z, const T* __restrict__ table, const int* __restrict__ tokens,
+                                      T* __restrict__ g, int T_, int D, int ld_table, int offset, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long n = (long long)T_ * D;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / D), d = (int)(i % D);
+        int tok = tokens[t];
+        tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+        const float v = ldf(z + i);
+        const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+        const float act = 0.5f * v * (1.0f + tanhf(inner));
+        stf(g + i, act * ldf(table + (size_t)tok * ld_table + offset + d));
+    }
+}
+
+extern "C" int tb_gelu_mul_table(const void* z, const void* table, const int* tokens, void* g, int dtype, int T_, int D,
+                                 int ld_table, int offset, int V, cudaStream_t stream) {
+    TB_REQUIRE(T_ > 0 && D > 0 && V > 0 && offset >= 0 && offset + D <= ld_table, "gelu_mul_table: columns %d..%d of a table %d wide", offset, offset + D, ld_table);
+    const long long n = (long long)T_ * D, blocks = (n + 255) / 256;
+    const int grid = (int)(blocks < 8192 ? blocks : 8192);
+    if (dtype == TB_F32) tb_launch(gelu_mul_table_kernel<float>, grid, 256, 0, stream, (const float*)z, (const float*)table, tokens, (float*)g, T_, D, ld_table, offset, V);
+    else if (dtype == TB_BF16) tb_launch(gelu_mul_table_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)z, (const __nv_bfloat16*)table, tokens, (__nv_bfloat16*)g, T_, D, ld_table, offset, V);
+    else TB_REQUIRE(false, "gelu_mul_table: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("gelu_mul_table");
     return 0;
 }

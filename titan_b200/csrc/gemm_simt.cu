@@ -20,10 +20,15 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
-gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restrict__ out,
-                 int M, int N, int K, int ldx, int ldo) {
+gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restrict__ out_,
+                 int M, int N, int K, int ldx, int ldo, long long sx, long long sw, long long so) {
     pdl_launch_dependents();
     pdl_wait();
+    // blockIdx.z: one of a batch of products of equal shape (the heads of a mixer, say), each at its own offset
+    X += (size_t)blockIdx.z * sx;
+    W += (size_t)blockIdx.z * sw;
+    void* out = (EPI == TB_EPI_STORE || EPI == TB_EPI_SWIGLU) ? (void*)((T*)out_ + (size_t)blockIdx.z * so)
+                                                              : (void*)((float*)out_ + (size_t)blockIdx.z * so);
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -88,15 +93,15 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restr
 
 template <typename T>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
-           cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           int batch, long long sx, long long sw, long long so, cudaStream_t stream) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     switch (epi) {
-        case TB_EPI_STORE: tb_launch(gemm_simt_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_F32: tb_launch(gemm_simt_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_ADD: tb_launch(gemm_simt_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_SWIGLU: tb_launch(gemm_simt_kernel<T, TB_EPI_SWIGLU>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
+        case TB_EPI_STORE: tb_launch(gemm_simt_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
+        case TB_EPI_F32: tb_launch(gemm_simt_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
+        case TB_EPI_ADD: tb_launch(gemm_simt_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
+        case TB_EPI_SWIGLU: tb_launch(gemm_simt_kernel<T, TB_EPI_SWIGLU>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
         default: tb_set_error("gemm: unknown epilogue %d", epi); return 1;
     }
     return 0;
@@ -104,18 +109,25 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx
 
 }  // namespace
 
-// ldx: row stride of X in elements; ldo: row stride of out in elements.
-extern "C" int tb_gemm_simt(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
-                            int ldo, int epi, cudaStream_t stream) {
+// ldx: row stride of X in elements; ldo: row stride of out in elements.  ``batch`` products of the same shape in one
+// launch: product z reads X + z * sx and W + z * sw and writes out + z * so (offsets in elements).
+extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
+                                    int ldo, int epi, int batch, long long sx, long long sw, long long so, cudaStream_t stream) {
     TB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: sizes must be positive (M=%d N=%d K=%d)", M, N, K);
+    TB_REQUIRE(batch > 0 && batch <= 65535, "gemm: a batch of %d products", batch);
     TB_REQUIRE(ldx >= K, "gemm: row stride %d of X is shorter than K=%d", ldx, K);
     TB_REQUIRE(epi != TB_EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N, found %d", N);
     TB_REQUIRE((M + BM - 1) / BM <= 65535, "gemm: M=%d is too large for one launch", M);
     int rc;
-    if (dtype == TB_F32) rc = launch<float>(X, W, out, M, N, K, ldx, ldo, epi, stream);
-    else if (dtype == TB_BF16) rc = launch<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, stream);
+    if (dtype == TB_F32) rc = launch<float>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
+    else if (dtype == TB_BF16) rc = launch<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
     else { tb_set_error("gemm: unknown dtype %d", dtype); return 1; }
     if (rc) return rc;
     TB_CHECK_LAUNCH("gemm_simt");
     return 0;
+}
+
+extern "C" int tb_gemm_simt(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
+                            int ldo, int epi, cudaStream_t stream) {
+    return tb_gemm_simt_batched(X, W, out, dtype, M, N, K, ldx, ldo, epi, 1, 0, 0, 0, stream);
 }

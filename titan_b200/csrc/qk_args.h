@@ -11,7 +11,16 @@ struct TbRotary {
     int rot;                                // leading dims of a head that are rotated
     float offset;                           // added to every position (0 for plain rotary)
     float magnitude;                        // factor on cosines and sines (1 for plain rotary)
+    int adjacent;                           // 0: dimension k is paired with k + rot/2; 1: dimension 2k with 2k + 1 (both turn by angle_k)
 };
+
+// Element e (< rot) of a rotated row: x[e] cos(angle_k) -/+ x[partner] sin(angle_k), where the first member of a pair
+// takes the minus.  Gives the pair's index k, the partner's index and the sign for either pairing.
+__host__ __device__ __forceinline__ void tb_rotary_pair(const TbRotary& r, int e, int* k, int* partner, float* sign) {
+    const int half = r.rot >> 1;
+    if (r.adjacent) { *k = e >> 1; *partner = e ^ 1; *sign = (e & 1) ? 1.f : -1.f; }
+    else { *k = e < half ? e : e - half; *partner = e < half ? e + half : e - half; *sign = e < half ? -1.f : 1.f; }
+}
 
 struct QkArgs {
     const void* in; int in_stride;          // [T][in_stride]: Q | K | V

@@ -114,6 +114,9 @@ class StepContext:
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # long-lived buffers by name
 
     sites_taken: int = 0               # places of "row_sums" handed out in this step
+    run: int = 0                       # which run of the layer order is at work (set by the model)
+    carried: Dict[object, object] = field(default_factory=dict)     # what parts hand on within THIS step (a cache owner's rows for its readers, ...)
+    after_blocks: List[object] = field(default_factory=list)        # callables the model runs once after the last block (appends that had to wait)
 
     def row_sums(self) -> Optional[torch.Tensor]:
         """A float32 [16, 32] place of this step's own, for a product that leaves its rows' partial sums of squares

@@ -27,6 +27,7 @@ class DecoderModel:
         self.blocks = [build_block(layer) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm)
         self.embedding: Optional[torch.Tensor] = None
+        self.shared = {}
         self.lm_head: Optional[torch.Tensor] = None
 
     def declared_weights(self) -> List[WeightSpec]:
@@ -45,8 +46,11 @@ class DecoderModel:
         by_name = {w.name: w for w in self.declared_weights()}
         get = lambda name: source.get(by_name[name])
         self.embedding = get(self.spec.embedding)
+        self.shared = {name: get(name) for name, _ in self.spec.shared_tensors}
         for b in self.blocks:
             b.bind(get)
+            if hasattr(b, "bind_shared"):
+                b.bind_shared(self.shared)
         self.final_norm.bind(get)
         self.lm_head = self.embedding if self.spec.lm_head is None else get(self.spec.lm_head)
 
@@ -78,7 +82,11 @@ class DecoderModel:
         if "row_sums" not in ctx.scratch:      # places where folded norms leave sums of squares: one per run of a layer
             ctx.scratch["row_sums"] = torch.zeros((len(self.spec.order), 16, 32), dtype=torch.float32, device=ctx.device)
         for run, i in enumerate(self.spec.order):
+            ctx.run = run
             self.blocks[i].forward(x, ctx, cache.view_for_layer(self.cache_run_of(run)))
+        for late in ctx.after_blocks:          # cache rows that a later layer of the step still had to read as they were
+            late()
+        ctx.after_blocks.clear()
         return x
 
     def logits(self, x: torch.Tensor, ctx, rows: torch.Tensor) -> torch.Tensor:

@@ -64,7 +64,7 @@ class Batch(Structure):
 class RotaryArgs(Structure):
     """What a position encoding hands to the kernels; a mixer passes it on without looking inside.
     angle_k(position) = (position + offset) * inv_freq[k]; cosines and sines are scaled by ``magnitude``."""
-    _fields_ = [("inv_freq", c_void_p), ("rot", c_int), ("offset", c_float), ("magnitude", c_float)]
+    _fields_ = [("inv_freq", c_void_p), ("rot", c_int), ("offset", c_float), ("magnitude", c_float), ("adjacent", c_int)]
 
 
 class QkArgs(Structure):
@@ -81,7 +81,25 @@ class AttnArgs(Structure):
                 ("out", c_void_p), ("out_stride", c_int), ("cache", KvView), ("batch", Batch),
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
-                ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs))]
+                ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs)),
+                ("hd_v", c_int), ("v_alias", c_int)]
+
+
+class LatentArgs(Structure):
+    """Arguments of the kernel between the input projection of a latent-attention mixer and its attention (csrc/latent.cu)."""
+    _fields_ = [("inp", c_void_p), ("in_stride", c_int), ("q_nope", c_void_p), ("qn_stride", c_int),
+                ("q_abs", c_void_p), ("qa_stride", c_int), ("kv_rows", c_void_p), ("kv_stride", c_int),
+                ("latent_w", c_void_p), ("eps", c_float), ("rope", RotaryArgs),
+                ("H", c_int), ("dn", c_int), ("rd", c_int), ("r", c_int), ("dk", c_int), ("owner", c_int),
+                ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p), ("kv_len", c_void_p),
+                ("cache", KvView), ("append", c_int), ("T", c_int)]
+
+
+class LightningArgs(Structure):
+    """Arguments of the decayed linear-attention recurrence (csrc/lightning.cu)."""
+    _fields_ = [("proj", c_void_p), ("stride", c_int), ("out", c_void_p), ("out_stride", c_int), ("state", c_void_p),
+                ("decay", c_void_p), ("q_start", c_void_p), ("slot_of_seq", c_void_p),
+                ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int)]
 
 
 class SampleArgs(Structure):
@@ -108,6 +126,22 @@ def lib():
         l.tb_scale_f32.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_longlong, c_longlong, c_longlong, c_void_p]
+        l.tb_rmsnorm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        l.tb_round_rows.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p]
+        l.tb_gelu_mul_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_latent_prep.argtypes = [POINTER(LatentArgs), c_int, c_void_p]
+        l.tb_latent_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
+        l.tb_lightning_scan.argtypes = [POINTER(LightningArgs), c_int, c_void_p]
+        l.tb_gated_rmsnorm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        l.tb_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_moe_plan_tiles.argtypes = [c_int, c_int]
+        l.tb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_moe_grouped.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_moe_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
@@ -217,6 +251,124 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, str
         raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(lib().tb_gemm_simt(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K,
                               x.stride(0), out.stride(0), epi, stream))
+
+
+def gemm_simt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, batch: int,
+                      x_step: int, out_step: int) -> None:
+    """``batch`` products of one shape in one launch: out_z (epilogue ``epi``) = x_z[M,K] . w[z][N,K]^T, where x_z and
+    out_z are the views ``x`` and ``out`` moved right by z * x_step and z * out_step columns (the heads of a mixer, side
+    by side in the rows of one buffer) and ``w`` is [batch, N, K]."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    if w.dim() != 3 or w.shape[0] != batch or w.shape[2] != K or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_batched: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
+    N = w.shape[1]
+    _check(lib().tb_gemm_simt_batched(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K, x.stride(0),
+                                      out.stride(0), epi, batch, x_step, N * K, out_step, stream))
+
+
+def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, x: torch.Tensor, eps: float, stream: int,
+                lowp: Optional[torch.Tensor] = None, zero_y: bool = True) -> None:
+    """x += y / sqrt(mean(y^2) + eps) * w (float32 rows): a norm on a sublayer's output, added to the residual stream.
+    ``zero_y`` leaves y zeroed for the next sublayer's products to add into; ``lowp`` receives the new rows of x rounded
+    to its dtype (what the next sublayer's first product reads)."""
+    _need_cuda(y, w, x, lowp)
+    if y.dtype != torch.float32 or x.dtype != torch.float32 or w.dtype != torch.float32 or y.shape != x.shape \
+            or not (y.is_contiguous() and x.is_contiguous()) or (lowp is not None and (lowp.shape != x.shape or not lowp.is_contiguous())):
+        raise KernelError("rmsnorm_add: contiguous float32 rows of one shape are wanted")
+    _check(lib().tb_rmsnorm_add(y.data_ptr(), w.data_ptr(), x.data_ptr(), _ptr(lowp), dtype_code(lowp.dtype) if lowp is not None else F32,
+                                x.shape[0], x.shape[1], eps, int(zero_y), stream))
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor, stream: int) -> None:
+    """out = x rounded to bfloat16 (x float32, both contiguous and of one shape)."""
+    _need_cuda(x, out)
+    if x.dtype != torch.float32 or out.dtype != torch.bfloat16 or x.shape != out.shape or not (x.is_contiguous() and out.is_contiguous()):
+        raise KernelError("round_rows: float32 in, bfloat16 out, one shape, contiguous")
+    _check(lib().tb_round_rows(x.data_ptr(), out.data_ptr(), x.numel(), stream))
+
+
+def gelu_mul_table(z: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, offset: int, g: torch.Tensor, stream: int) -> None:
+    """g[t] = gelu_tanh(z[t]) * table[tokens[t], offset : offset + D]  (z, g [T, D] and the table in one dtype)."""
+    _need_cuda(z, table, tokens, g)
+    if not (z.is_contiguous() and g.is_contiguous() and table.is_contiguous()) or z.dtype != table.dtype or g.dtype != z.dtype:
+        raise KernelError("gelu_mul_table: contiguous tensors of one dtype are wanted")
+    _check(lib().tb_gelu_mul_table(z.data_ptr(), table.data_ptr(), tokens.data_ptr(), g.data_ptr(), dtype_code(z.dtype), z.shape[0],
+                                   z.shape[1], table.shape[1], int(offset), table.shape[0], stream))
+
+
+def latent_prep(args: "LatentArgs", out_dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_latent_prep(byref(args), dtype_code(out_dtype), stream))
+
+
+def latent_append(rows: torch.Tensor, cache: KvView, batch: Batch, stream: int) -> None:
+    _check(lib().tb_latent_append(rows.data_ptr(), rows.stride(0), dtype_code(rows.dtype), byref(cache), byref(batch), stream))
+
+
+def lightning_scan(args: "LightningArgs", dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_lightning_scan(byref(args), dtype_code(dtype), stream))
+
+
+def gated_rmsnorm(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, y: torch.Tensor, eps: float, stream: int) -> None:
+    """y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate), row by row; o float32, gate and y in the compute dtype (row-strided views allowed)."""
+    _need_cuda(o, w, gate, y)
+    if o.dtype != torch.float32 or gate.dtype != y.dtype or o.stride(1) != 1 or gate.stride(1) != 1 or y.stride(1) != 1:
+        raise KernelError("gated_rmsnorm: float32 rows in, gate and output of one dtype")
+    _check(lib().tb_gated_rmsnorm(o.data_ptr(), o.stride(0), w.data_ptr(), gate.data_ptr(), gate.stride(0), y.data_ptr(), y.stride(0),
+                                  dtype_code(y.dtype), o.shape[0], o.shape[1], eps, stream))
+
+
+def moe_route(z: torch.Tensor, experts: int, top: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
+              gate: Optional[torch.Tensor], stream: int) -> None:
+    """Per row of z (float32 [T, experts (+1)]): the ``top`` largest logits' indices and their softmax weights; the last
+    column's sigmoid into ``gate`` if the row has one more column than experts."""
+    _need_cuda(z, ids, wts, gate)
+    _check(lib().tb_moe_route(z.data_ptr(), z.stride(0), experts, top, int(has_gate), ids.data_ptr(), wts.data_ptr(), _ptr(gate),
+                              z.shape[0], stream))
+
+
+def moe_plan_tiles(pairs: int, experts: int) -> int:
+    return int(lib().tb_moe_plan_tiles(pairs, experts))
+
+
+def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor, stream: int):
+    """Groups the (token, choice) pairs by expert.  ``plan`` is int32 scratch of at least 2 P + 3 tiles + 1; returns the
+    views (perm, tile_e, tile_row0, tile_rows, n_tiles, max_tiles) the grouped product takes."""
+    P = ids.numel()
+    tiles = moe_plan_tiles(P, experts)
+    if plan.numel() < 2 * P + 3 * tiles + 1:
+        raise KernelError("moe_plan: the plan's buffer is too small")
+    rank, perm = plan[:P], plan[P:2 * P]
+    te, tr0, trn = (plan[2 * P + i * tiles: 2 * P + (i + 1) * tiles] for i in range(3))
+    n = plan[2 * P + 3 * tiles: 2 * P + 3 * tiles + 1]
+    _check(lib().tb_moe_plan(ids.data_ptr(), P, experts, rank.data_ptr(), perm.data_ptr(), te.data_ptr(), tr0.data_ptr(),
+                             trn.data_ptr(), n.data_ptr(), tiles, stream))
+    return perm, te, tr0, trn, n, tiles
+
+
+def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, plan, top: int, stream: int) -> None:
+    """The experts' products over the plan's tiles on the CUDA cores.  mode 0: x [T, K] tokens, w [E, 2F, K] (gate and up
+    rows interleaved), out [P, F] in sorted order; mode 1: x [P, K] sorted rows, w [E, N, K], out float32 [P, N] in pair order."""
+    _need_cuda(x, w, out)
+    perm, te, tr0, trn, n, tiles = plan
+    _check(lib().tb_moe_grouped(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), dtype_code(w.dtype), mode,
+                                perm.data_ptr(), te.data_ptr(), tr0.data_ptr(), trn.data_ptr(), n.data_ptr(), tiles,
+                                w.shape[1], w.shape[2], top, stream))
+
+
+def moe_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ids: torch.Tensor, top: int, stream: int) -> None:
+    """The same two products for a few pairs, a warp per output, without a plan (pair order in and out)."""
+    _need_cuda(x, w, out, ids)
+    n_out = w.shape[1] // 2 if mode == 0 else w.shape[1]
+    _check(lib().tb_moe_rows(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), dtype_code(w.dtype), mode,
+                             ids.data_ptr(), ids.numel(), n_out, w.shape[2], top, stream))
+
+
+def moe_combine(y: torch.Tensor, wts: torch.Tensor, shared_y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                out: torch.Tensor, top: int, stream: int) -> None:
+    """out[t] += sum_k wts[t, k] * y[t * top + k] (+ gate[t] * shared_y[t]); everything float32."""
+    _need_cuda(y, wts, shared_y, gate, out)
+    _check(lib().tb_moe_combine(y.data_ptr(), wts.data_ptr(), _ptr(shared_y), _ptr(gate), out.data_ptr(), out.shape[0], out.shape[1], top, stream))
 
 
 def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> bool:

@@ -6,7 +6,7 @@ from typing import List
 from ..weights.loader import WeightSpec
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, Registry)
-from . import attention, block, mlp, norm, rotary  # noqa: F401  (registration)
+from . import attention, block, latent_attention, lightning, mlp, moe, norm, rotary, token_table  # noqa: F401  (registration)
 
 
 def build_block(layer_spec):
@@ -19,6 +19,7 @@ def build_block(layer_spec):
 def declare_weights(model_spec) -> List[WeightSpec]:
     """Every tensor the model owns, in file order, without touching a device."""
     specs = [WeightSpec(model_spec.embedding, (model_spec.vocab_size, model_spec.hidden_size))]
+    specs += [WeightSpec(name, tuple(shape)) for name, shape in model_spec.shared_tensors]
     for layer in model_spec.layers:
         specs += build_block(layer).weight_specs()
     specs += NORMS.build(model_spec.final_norm).weight_specs("")

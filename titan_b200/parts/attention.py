@@ -83,6 +83,8 @@ class AttentionMixer(Mixer):
         self.Q, self.KV = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         self.shared = s.cache_from is not None
         self.position = POSITIONS.build(s.position)
+        if getattr(s.position, "pairing", "half") != "half" and s.position.kind == "rope":
+            raise ValueError("grouped-query attention rotates the pairs (k, k + rotary_dim/2) only")
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
         self._views = {}

@@ -56,3 +56,79 @@ class PreNormBlock(Part):
 
 
 BLOCKS.register("pre_norm", PreNormBlock)
+
+
+class OutputNormBlock(Part):
+    """``output_norm``: every sublayer reads the residual stream itself and its OUTPUT is normed before it is added:
+
+        x += norm1(mixer(x));  x += norm2(feed_forward(x));  x += norm_k(extra_k(x)) for every further sublayer
+
+    The feed-forward (with its norm) may be absent.  Further sublayers are feed-forward parts named in
+    ``LayerSpec.extra`` under "sublayers" (a tuple of FeedForwardSpec), their norms are ``LayerSpec.norms`` in the same
+    order.  A sublayer adds into a zeroed float32 buffer of the step; one kernel then norms that buffer's rows, adds them
+    to the residual stream, leaves the buffer zeroed for the next sublayer and, in bfloat16, writes the new rows rounded
+    for the next sublayer's first product (in float32 the sublayers read the residual stream in place)."""
+
+    def __init__(self, spec):
+        if spec.mixer_norm is None or (spec.feed_forward is None) != (spec.feed_forward_norm is None):
+            raise ValueError("the output_norm arrangement takes a mixer with its norm, and a feed-forward with its norm or neither")
+        self.spec = spec
+        self.mixer = MIXERS.build(spec.mixer)
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.feed_forward = None if spec.feed_forward is None else FEED_FORWARDS.build(spec.feed_forward)
+        self.feed_forward_norm = None if spec.feed_forward_norm is None else NORMS.build(spec.feed_forward_norm)
+        more = tuple(spec.option("sublayers", ()))
+        if len(more) != len(spec.norms):
+            raise ValueError(f"{len(more)} further sublayers with {len(spec.norms)} norms")
+        self.more = [(FEED_FORWARDS.build(f), NORMS.build(n)) for f, n in zip(more, spec.norms)]
+
+    def parts(self):
+        first = (self.mixer, self.mixer_norm) + (() if self.feed_forward is None else (self.feed_forward, self.feed_forward_norm))
+        return first + tuple(p for pair in self.more for p in pair)
+
+    def weight_specs(self, prefix: str = "") -> List[WeightSpec]:
+        out: List[WeightSpec] = []
+        for part in self.parts():
+            out += part.weight_specs(self.spec.prefix)
+        return out
+
+    def bind(self, get) -> None:
+        for part in self.parts():
+            part.bind(lambda name: get(self.spec.prefix + name))
+
+    def bind_shared(self, shared) -> None:
+        for part in self.parts():
+            if hasattr(part, "bind_shared"):
+                part.bind_shared(shared)
+
+    def _input(self, x, ctx):
+        """The residual rows as a sublayer's first product reads them: x itself in float32; in bfloat16 the rounded copy
+        that the kernel before left (if it was made for exactly this state of x), else one made now."""
+        if ctx.dtype == torch.float32:
+            return x, None
+        kept = ctx.carried.pop("rounded_rows", None)
+        if kept is not None and kept[1] == ctx.run and kept[0].shape == x.shape:
+            return kept[0], kept[0]
+        from .. import kernels as K
+        h = ctx.empty(tuple(x.shape))
+        K.round_rows(x, h, ctx.stream)
+        return h, h
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        from .. import kernels as K
+        y = ctx.carried.get("sublayer_sum")
+        if y is None or y.shape != x.shape:
+            y = ctx.carried["sublayer_sum"] = torch.zeros_like(x)         # zeroed once a step; the norm kernel leaves it zeroed
+        h, lowp = self._input(x, ctx)
+        steps = [(lambda: self.mixer.forward(h, ctx, cache, y), self.mixer_norm)]
+        if self.feed_forward is not None:
+            steps.append((lambda: self.feed_forward.forward(h, ctx, y), self.feed_forward_norm))
+        steps += [((lambda part=part: part.forward(h, ctx, y)), norm) for part, norm in self.more]
+        for run_sublayer, norm in steps:
+            run_sublayer()
+            K.rmsnorm_add(y, norm.weight, x, norm.spec.eps, ctx.stream, lowp=lowp, zero_y=True)
+        if lowp is not None:
+            ctx.carried["rounded_rows"] = (lowp, ctx.run + 1)             # valid for the next run of the order, if nothing else touches x
+
+
+BLOCKS.register("output_norm", OutputNormBlock)

@@ -1,0 +1,106 @@
+"""Mixture of experts as a feed-forward.
+
+    z = h . W_router^T (float32);  the ``top`` largest entries of z choose a token's experts, and their weights are the
+    softmax over the chosen entries only;  out += sum_k weight_k * expert_{e_k}(h)  (+ sigmoid(h . w_sg) * shared(h))
+    expert(h) = W_down (silu(W_gate h) * (W_up h))
+
+The router and the shared expert's gate are one float32 product ([E (+1), H]).  Every expert's gate and up rows are
+interleaved at bind time ([E, 2F, H]) so that one product applies the activation in its epilogue, as the gated MLP does.
+Routing, grouping and the experts' products all happen on the device: nothing is read on the host, so decode steps
+are captured as graphs.  A step with few (token, choice) pairs runs a warp-per-output kernel that reads each chosen
+expert's rows once (a decode step is bound by those bytes); larger steps group the pairs by expert
+(``moe_plan``) and run tiles of rows of one expert each (``moe_grouped``).
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..weights.loader import WeightSpec
+from .. import kernels as K
+from . import linear
+from .base import FEED_FORWARDS, FeedForward
+
+
+class MixtureOfExperts(FeedForward):
+    def __init__(self, spec):
+        s = spec
+        if s.activation != "silu":
+            raise ValueError(f"activation '{s.activation}' is not supported (only 'silu')")
+        self.spec = s
+        self.E, self.top, self.F = int(s.option("experts", 0)), int(s.option("top", 0)), s.intermediate_size
+        self.shared_F = int(s.option("shared_size", 0))
+        if self.E <= 0 or not 0 < self.top <= self.E or self.F <= 0:
+            raise ValueError(f"a mixture of {self.E} experts of size {self.F}, {self.top} a token")
+        self.w_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
+
+    def _names(self):
+        s = self.spec
+        names = {role: s.name(role, role) for role in ("gate", "up", "down", "router")}
+        names["expert"] = s.name("expert", "e{}.")              # prefix of expert number {}
+        names["shared"] = s.name("shared", "shared.")
+        names["shared_gate"] = s.name("shared_gate", "shared.sg")
+        return names
+
+    def weight_specs(self, prefix: str) -> List[WeightSpec]:
+        s, p, n = self.spec, prefix + self.spec.prefix, self._names()
+        H = s.hidden_size
+        specs = []
+        for e in range(self.E):
+            q = p + n["expert"].format(e)
+            specs += [WeightSpec(q + n["gate"], (self.F, H)), WeightSpec(q + n["up"], (self.F, H)), WeightSpec(q + n["down"], (H, self.F))]
+        specs.append(WeightSpec(p + n["router"], (self.E, H)))
+        if self.shared_F:
+            q = p + n["shared"]
+            specs += [WeightSpec(q + n["gate"], (self.shared_F, H)), WeightSpec(q + n["up"], (self.shared_F, H)),
+                      WeightSpec(q + n["down"], (H, self.shared_F)), WeightSpec(p + n["shared_gate"], (1, H))]
+        return specs
+
+    def bind(self, get) -> None:
+        s, p, n = self.spec, self.spec.prefix, self._names()
+        H = s.hidden_size
+        first = get(p + n["expert"].format(0) + n["gate"])
+        self.w_gate_up = torch.empty((self.E, 2 * self.F, H), dtype=first.dtype, device=first.device)
+        self.w_down = torch.empty((self.E, H, self.F), dtype=first.dtype, device=first.device)
+        for e in range(self.E):
+            q = p + n["expert"].format(e)
+            self.w_gate_up[e, 0::2] = get(q + n["gate"])
+            self.w_gate_up[e, 1::2] = get(q + n["up"])
+            self.w_down[e] = get(q + n["down"])
+        router = get(p + n["router"])
+        if self.shared_F:
+            q = p + n["shared"]
+            self.w_router = torch.cat([router, get(p + n["shared_gate"])], dim=0).contiguous()
+            self.ws_gate_up = torch.stack([get(q + n["gate"]), get(q + n["up"])], dim=1).reshape(2 * self.shared_F, H).contiguous()
+            self.ws_down = get(q + n["down"])
+        else:
+            self.w_router = router
+
+    def forward(self, h, ctx, out: torch.Tensor) -> None:
+        T, H, top, E = h.shape[0], self.spec.hidden_size, self.top, self.E
+        P = T * top
+        f32, i32 = torch.float32, torch.int32
+        z = ctx.empty((T, self.w_router.shape[0]), f32)
+        linear.matmul(h, self.w_router, z, linear.EPI_F32, ctx)
+        ids, wts = ctx.empty((T, top), i32), ctx.empty((T, top), f32)
+        gate = ctx.empty((T,), f32) if self.shared_F else None
+        K.moe_route(z, E, top, bool(self.shared_F), ids, wts, gate, ctx.stream)
+        shared_y = None
+        if self.shared_F:
+            act_s = ctx.empty((T, self.shared_F))
+            linear.matmul(h, self.ws_gate_up, act_s, linear.EPI_SWIGLU, ctx)
+            shared_y = ctx.empty((T, H), f32)
+            linear.matmul(act_s, self.ws_down, shared_y, linear.EPI_F32, ctx)
+        act, y = ctx.empty((P, self.F)), ctx.empty((P, H), f32)
+        if P <= int(ctx.options.get("moe_rows_pairs", 64)):
+            K.moe_rows(h, self.w_gate_up, act, 0, ids, top, ctx.stream)
+            K.moe_rows(act, self.w_down, y, 1, ids, top, ctx.stream)
+        else:
+            plan = K.moe_plan(ids, E, ctx.empty((2 * P + 3 * K.moe_plan_tiles(P, E) + 1,), i32), ctx.stream)
+            K.moe_grouped(h, self.w_gate_up, act, 0, plan, top, ctx.stream)
+            K.moe_grouped(act, self.w_down, y, 1, plan, top, ctx.stream)
+        K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream)
+
+
+FEED_FORWARDS.register("moe", MixtureOfExperts)

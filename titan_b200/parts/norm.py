@@ -1,4 +1,5 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, float32 inside, weight used as stored.
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * (offset + w), float32 inside; offset 0 uses the weight as stored,
+offset 1 is for checkpoints that store the weight's deviation from one (``NormSpec.weight_offset``).
 
 berniehans/titan: engine/engine-core/src/forward_cpu.rs:189-200 (eps inside the
 sqrt; no ``1 + w``); kernel engine/engine-cuda/kernels/norm_rope.cu:37-80.
@@ -40,10 +41,13 @@ class RMSNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
-        return [WeightSpec(prefix + self.spec.weight, (self.spec.size,), "vector", ("one_plus_normal", 0.1))]
+        init = "one_plus_normal" if self.spec.weight_offset == 0.0 else "normal"      # a weight stored around zero is drawn around zero
+        return [WeightSpec(prefix + self.spec.weight, (self.spec.size,), "vector", (init, 0.1))]
 
     def bind(self, get) -> None:
-        self.weight = get(self.spec.weight)
+        w = get(self.spec.weight)
+        # the factor on a row is (offset + stored weight), formed once, in float32
+        self.weight = w if self.spec.weight_offset == 0.0 else (w.float() + float(self.spec.weight_offset)).contiguous()
 
     def deferred(self, x: torch.Tensor, ctx) -> DeferredNorm:
         return DeferredNorm(self, x, ctx)

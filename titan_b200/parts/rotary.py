@@ -1,8 +1,11 @@
 """Position encodings that a mixer applies to its queries and keys.
 
-``rope``: half-split rotary over the first ``rotary_dim`` dims of a head:
-for k < rotary_dim/2, angle = position * theta^(-2k/rotary_dim), and the pair
-(k, k + rotary_dim/2) is rotated (berniehans/titan:
+``rope``: rotary over the first ``rotary_dim`` dims of a head: for
+k < rotary_dim/2, angle = position * theta^(-2k/rotary_dim), and a pair of
+dimensions turns by it: (k, k + rotary_dim/2) with ``pairing="half"``,
+(2k, 2k + 1) with ``pairing="adjacent"`` (which kernels take which pairing is
+the mixers' business: grouped-query attention takes "half", latent attention
+either) (berniehans/titan:
 engine/engine-core/src/forward_cpu.rs:226-241; rotary_dim = head_dim,
 forward_driver.rs:608).  The inverse frequencies are computed in float64 on the
 host and rounded once to float32; the angle and its sine and cosine are float32
@@ -21,8 +24,8 @@ from .base import POSITIONS, PositionEncoding
 
 class Rotary(PositionEncoding):
     def __init__(self, spec):
-        if spec.pairing != "half":
-            raise ValueError(f"rotary pairing '{spec.pairing}' is not supported (only 'half')")
+        if spec.pairing not in ("half", "adjacent"):
+            raise ValueError(f"rotary pairing '{spec.pairing}' is not supported ('half' or 'adjacent')")
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be positive and even")
         self.spec = spec
@@ -31,6 +34,11 @@ class Rotary(PositionEncoding):
     @property
     def rotary_dim(self) -> int:
         return self.spec.rotary_dim
+
+    def kernel_args(self, device):
+        args = super().kernel_args(device)
+        args.adjacent = int(self.spec.pairing == "adjacent")
+        return args
 
     def tables(self, device) -> Dict[str, torch.Tensor]:
         if not self._tables:

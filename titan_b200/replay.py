@@ -35,8 +35,10 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
 
     print("[titan_b200] loading the engine (kernels are compiled on the first call)", file=sys.stderr, flush=True)
+    from .cache import PAGE_SIZE
     from .engine import Engine, StepEntry
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    # room for what the live requests hold, each rounded up to whole pages, and a few pages to spare
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 8 * PAGE_SIZE)
     print(f"[titan_b200] ready: {engine.spec.architecture}, {args.dtype}, cache of {engine.cache.num_pages} pages",
           file=sys.stderr, flush=True)
     slots: Dict[str, int] = {}

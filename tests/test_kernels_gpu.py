@@ -390,7 +390,7 @@ def test_attention_refuses_bad_heads(K):
     a.nh, a.nkv, a.hd = 5, 2, 32
     with pytest.raises(K.KernelError, match="multiple"):
         K.attn_prefill(a, torch.float32, stream())
-    a.nh, a.nkv, a.hd = 4, 2, 272
+    a.nh, a.nkv, a.hd = 4, 2, 1032          # rows of up to 1,024 elements are taken
     with pytest.raises(K.KernelError, match="head_dim"):
         K.attn_prefill(a, torch.float32, stream())
 

@@ -564,6 +564,117 @@ def micro():
     return 0
 
 
+# ------------------------------------------------------------------ another design beside the closest existing model
+def tefezen_config(width, layers, heads, experts, top, ff, shared_ff, window, vocab=32768, side=128):
+    """A Tefezen model of sizes that resemble a served model's layers: layers alternate latent attention over a window
+    (every second of them reading the first one's latents) and lightning attention; every layer has a mixture of experts."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared_ff}}
+    out, first_latent = [], None
+    for i in range(layers):
+        if i % 2 == 0:
+            m = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "mask": {"size": window},
+                 "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / (192 ** 0.5)}
+            if first_latent is None:
+                first_latent = i
+            elif (i // 2) % 2 == 1:
+                m["kv_from"] = first_latent
+            out.append({"type": "latent_attention", "mixer": m, "mlp": moe})
+        else:
+            decay = [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads - 1)) for h in range(heads)]
+            out.append({"type": "lightning", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay}, "mlp": moe})
+    return {"architecture": "Tefezen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "token_side": {"dim": side}, "layers": out}
+
+
+def qwen3_like(width, layers, heads, ffn, vocab=32768):
+    """The dense model of equal size: the same width, depth and heads, and a feed-forward as wide as what one token uses
+    of the mixture (its chosen experts and the shared one)."""
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=layers, hidden_size=width,
+                num_attention_heads=heads, num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=ffn, vocab_size=vocab,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=8192)
+
+
+def launcher_times(engine, torch, K, entries):
+    """Device time of every launcher call of one eager step, by launcher name (CUDA events around each call; the calls of
+    one name added up): {name: (calls, microseconds)}."""
+    names = [n for n in ("embed", "scale_f32", "rmsnorm", "rmsnorm_add", "round_rows", "gelu_mul_table", "gemm_simt", "gemm_simt_batched",
+                         "gemm_tc", "gemm_tc_normed", "qk_norm_rope", "kv_append", "attn_prefill", "attn_decode", "attn_decode_mma",
+                         "attn_prefill_mma", "attn_prefill_tc", "latent_prep", "latent_append", "lightning_scan", "lightning_chunks",
+                         "gated_rmsnorm", "moe_route", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc") if hasattr(K, n)]
+    events, originals = [], {n: getattr(K, n) for n in names}
+
+    def wrap(name, f):
+        def g(*a, **k):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            r = f(*a, **k)
+            a1.record()
+            events.append((name, a0, a1))
+            return r
+        return g
+    for n, f in originals.items():
+        setattr(K, n, wrap(n, f))
+    try:
+        engine.step(entries)
+        torch.cuda.synchronize()
+    finally:
+        for n, f in originals.items():
+            setattr(K, n, f)
+    out = {}
+    for name, a0, a1 in events:
+        calls, us = out.get(name, (0, 0.0))
+        out[name] = (calls + 1, us + a0.elapsed_time(a1) * 1e3)
+    return {k: (c, round(u, 1)) for k, (c, u) in out.items()}
+
+
+def run_design(args):
+    """``--design tefezen``: prompt and decode throughput of the Tefezen design at sizes that resemble a served model's
+    layers (random weights), beside the Qwen3 dense model of equal size, and where a step's time goes by launcher."""
+    import torch
+
+    from titan_b200 import Engine, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    pk = peaks()
+    T, kv = args.prefill_tokens, args.prompt_tokens
+    sizes = [dict(width=2048, layers=4, heads=16, experts=32, top=4, ff=1024, shared_ff=2048, window=1024),
+             dict(width=4096, layers=4, heads=32, experts=16, top=2, ff=2048, shared_ff=4096, window=2048)]
+    if args.design_size is not None:
+        sizes = [sizes[args.design_size]]
+    results = []
+    for sz in sizes:
+        row = {"size": sz}
+        for which in ("tefezen", "qwen3"):
+            if which == "tefezen":
+                cfg = tefezen_config(**sz)
+            else:
+                cfg = qwen3_like(sz["width"], sz["layers"], sz["heads"], sz["top"] * sz["ff"] + sz["shared_ff"])
+            engine = Engine.from_random(config_from_dict(cfg), 1, "bfloat16", max_tokens=8 * 4096 + 4096, max_context=4096, max_slots=10, max_batch=8)
+            med, best = time_prefill(engine, torch, T, 2, 3)
+            r = {"prefill_ms": round(med, 3), "prefill_tok_s": round(T / med * 1e3), "weight_bytes": engine.model.weight_bytes()}
+            for batch in (1, 8):
+                dev_ms, wall_ms, launches, _, _ = time_decode(engine, torch, K, batch, kv, min(args.steps, 64), args.warmup)
+                r[f"decode_b{batch}_ms"] = round(dev_ms, 4)
+                r[f"decode_b{batch}_e2e_ms"] = round(wall_ms, 4)
+                r[f"decode_b{batch}_tok_s"] = round(batch / dev_ms * 1e3)
+                r[f"decode_b{batch}_launches_per_step"] = launches // min(args.steps, 64)
+            s = engine.alloc_slot()
+            prompt = [(13 * i + 5) % engine.vocab_size for i in range(T)]
+            engine.step([StepEntry(s, prompt, [T - 1])])
+            engine.free_slot(s)
+            s = engine.alloc_slot()
+            r["prefill_launchers_us"] = launcher_times(engine, torch, K, [StepEntry(s, prompt, [T - 1])])
+            r["decode_b1_launchers_us"] = launcher_times(engine, torch, K, [StepEntry(s, [7], [0])])
+            engine.free_slot(s)
+            engine.check_kernels()
+            row[which] = r
+            del engine
+            torch.cuda.empty_cache()
+        results.append(row)
+    print(json.dumps({"design": "tefezen", "beside": "qwen3 dense of equal width, depth, heads and per-token feed-forward width", "dtype": "bf16",
+                      "data": "synthetic", "prefill_tokens": T, "decode_after_tokens": kv, "peaks": pk, "sizes": results}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -582,7 +693,14 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     ap.add_argument("--timeline", type=int, default=0, metavar="BATCH", help="when the CTAs of one captured decode step's kernels start, wait and end "
                     "(needs TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE); text lines, not the JSON line")
+    ap.add_argument("--design", default=None, choices=["tefezen"], help="prompt and decode throughput of another design at a few sizes beside "
+                    "the dense model of equal size; one JSON line of its own, the default workload is not run")
+    ap.add_argument("--design-size", type=int, default=None, choices=[0, 1], help="with --design: one of its sizes only")
     args = ap.parse_args()
+    if args.design:
+        if args.warmup < 3:
+            args.warmup = 3
+        return run_design(args)
     if args.profile_case:
         return profile_case(args.prompt_tokens)
     if args.micro:

@@ -133,6 +133,7 @@ def latent_spec(H, dn, rd, dv, r, window, rot_dims, scale, cache_window=None):
     (3, 16, 8, 24, 20, 20, 8),         # a ring of one page that long sequences go round several times
     (2, 8, 6, 8, 27, 64, 2),           # sizes that are no multiples of 8; a window of exactly one page; four unrotated dims
     (1, 24, 16, 16, 300, 130, 16),     # rows wider than 256: the attention kernels' wide instantiation
+    (3, 128, 64, 128, 96, 70, 64),     # the sizes whose whole prompts, in bfloat16, expand keys and values and take the tensor-core kernel
 ])
 def test_latent_attention_alone(dtype, H, dn, rd, dv, r, window, rot_dims):
     """Prompts of two sequences, a further portion (on a ring: its rows are appended after the step), then single

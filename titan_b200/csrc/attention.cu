@@ -154,8 +154,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     pdl_wait();
     extern __shared__ float q_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
-    const int hd = a.hd, hdv = value_width(a), group = a.nh / a.nkv;
+    const int blocks_y = a.head_blocks > 0 ? a.head_blocks : a.nkv;
+    const int b = blockIdx.x, kh = (int)blockIdx.y * a.nkv / blocks_y, split = blockIdx.z;
+    const int hd = a.hd, hdv = value_width(a), group = a.nh / blocks_y;
     const int len = a.batch.kv_len[b];
     const int keys = tb_split_keys(len, a.chunk, a.n_splits);
     if ((long long)split * keys >= len) return;     // the merge reads ceil(len / keys) splits only
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     const int lo = max(wlo, split * keys), hi = min(len, (split + 1) * keys);
     float* qs = q_smem + warp * hd;
     for (int g = warp; g < group; g += ATT_WARPS) {
-        const int h = kh * group + g;
+        const int h = (int)blockIdx.y * group + g;
         float* part = a.scratch + ((size_t)(b * a.nh + h) * a.n_splits + split) * (hdv + 2);
         Running<MAXE> st;
         st.m = -FLT_MAX; st.l = 0.f;
@@ -286,8 +287,10 @@ extern "C" int tb_attn_decode(const AttnArgs* args, int dtype, cudaStream_t stre
     TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_decode: unknown dtype %d", dtype);
     TB_REQUIRE(a.batch.B > 0 && a.cache.storage && a.scratch, "attn_decode: needs sequences, a cache and scratch");
     TB_REQUIRE(a.chunk > 0 && a.n_splits > 0 && a.n_splits <= 65535, "attn_decode: bad split (chunk=%d splits=%d)", a.chunk, a.n_splits);
-    TB_REQUIRE(a.nkv <= 65535, "attn_decode: too many kv heads");
-    dim3 grid(a.batch.B, a.nkv, a.n_splits), mgrid(a.batch.B, a.nh);
+    TB_REQUIRE(a.nkv <= 65535 && a.head_blocks <= 65535, "attn_decode: too many kv heads");
+    TB_REQUIRE(a.head_blocks == 0 || (a.head_blocks > 0 && a.nh % a.head_blocks == 0 && a.head_blocks % a.nkv == 0),
+               "attn_decode: %d blocks for %d query heads on %d kv heads", a.head_blocks, a.nh, a.nkv);
+    dim3 grid(a.batch.B, a.head_blocks > 0 ? a.head_blocks : a.nkv, a.n_splits), mgrid(a.batch.B, a.nh);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
     const bool wide = wide_rows(a);
     ATT_DISPATCH(attn_decode_kernel, grid, ATT_WARPS * 32, smem);

@@ -35,6 +35,11 @@ struct AttnArgs {
     // elements of its key row (one stored row per token serves as both: attention in a shared latent space, where
     // the key is [latent | rotated part] and the value the latent alone), so no V plane or V columns are read.
     int hd_v; int v_alias;
+    // Decode, the any-size kernel: how many blocks share the query heads of a launch (grid.y).  Zero: one block per kv
+    // head, whose warps take that head's query heads in turn.  A model with many query heads on one kv head (all heads
+    // over one shared latent) asks for more blocks: block y then takes heads [y * nh / head_blocks, (y + 1) * nh / head_blocks)
+    // and reads kv head y * nkv / head_blocks.  Must divide nh and be a multiple of nkv.
+    int head_blocks;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

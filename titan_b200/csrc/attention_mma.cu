@@ -489,19 +489,24 @@ struct PreArgs {
     int k_col0; int v_col0;                  // first column of the K heads and of the V heads
     // keys and values from the cache: first position of each sequence's rows, slots, block table, first V row of the map
     int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
+    int tail_col0;                           // HDT > 0: first column (in the tail map's rows) of the key dimensions that all heads share
 };
 
-template <int HD>
+// HDK: dimensions of a query and of a key; HDV: of a value and of an output row (the same for grouped-query attention).
+// HDT: the last HDT of a key's HDK dimensions are shared by all heads and come from a third buffer (``tail_map``, at
+// column tail_col0 of the token's row): a key that is [a part of its own head | a rotated part common to all heads].
+template <int HDK, int HDV, int HDT>
 __global__ void __launch_bounds__(DEC_THREADS, 2)
-attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __grid_constant__ CUtensorMap kv_map, PreArgs a) {
+attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __grid_constant__ CUtensorMap kv_map,
+                        const __grid_constant__ CUtensorMap tail_map, PreArgs a) {
     constexpr int STAGES = 2;
-    constexpr int BOXES = HD / 64;
-    constexpr uint32_t TILE_BYTES = 64 * HD * 2;
-    constexpr int KS = HD / 16, NT = HD / 8;
+    constexpr int BOXES_K = HDK / 64, BOXES_V = HDV / 64, BOXES_OWN = (HDK - HDT) / 64;
+    constexpr uint32_t K_BYTES = 64 * HDK * 2, V_BYTES = 64 * HDV * 2, STAGE_BYTES = K_BYTES + V_BYTES;
+    constexpr int KS = HDK / 16, NT = HDV / 8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_smem = base + STAGES * 2 * TILE_BYTES;
-    uint64_t* full = (uint64_t*)(q_smem + TILE_BYTES);
+    uint8_t* q_smem = base + STAGES * STAGE_BYTES;
+    uint64_t* full = (uint64_t*)(q_smem + K_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* qbar = empty + STAGES;
 
@@ -532,23 +537,24 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
 
     if (warp == DEC_WARPS) {
         if (lane == 0) {
-            mbar_expect_tx(qbar, TILE_BYTES);
+            mbar_expect_tx(qbar, K_BYTES);
 #pragma unroll
-            for (int x = 0; x < BOXES; ++x) tma_load_2d(q_smem + x * 8192, &qkv_map, qbar, h * HD + x * 64, tok0 + r0);
+            for (int x = 0; x < BOXES_K; ++x) tma_load_2d(q_smem + x * 8192, &qkv_map, qbar, h * HDK + x * 64, tok0 + r0);
             const int* tab = a.paged ? a.table + (size_t)a.slot_of_seq[seq] * a.table_width : nullptr;
-            const int kx = a.paged ? 0 : a.k_col0 + kh * HD, vx = a.paged ? 0 : a.v_col0 + kh * HD;
+            const int kx = a.paged ? 0 : a.k_col0 + kh * (HDK - HDT), vx = a.paged ? 0 : a.v_col0 + kh * HDV;
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 3);
-                uint8_t* kd = base + s * 2 * TILE_BYTES;
+                uint8_t* kd = base + s * STAGE_BYTES;
                 const int krow = a.paged ? (tab[kt0 + i] * a.nkv + kh) * 64 : tok0 + (kt0 + i) * 64;
                 const int vrow = a.paged ? a.v_row0 + krow : krow;
-                mbar_expect_tx(full + s, 2 * TILE_BYTES);
+                mbar_expect_tx(full + s, STAGE_BYTES);
 #pragma unroll
-                for (int x = 0; x < BOXES; ++x) {
-                    tma_load_2d(kd + x * 8192, a.paged ? &kv_map : &qkv_map, full + s, kx + x * 64, krow);
-                    tma_load_2d(kd + TILE_BYTES + x * 8192, a.paged ? &kv_map : &qkv_map, full + s, vx + x * 64, vrow);
-                }
+                for (int x = 0; x < BOXES_OWN; ++x) tma_load_2d(kd + x * 8192, &kv_map, full + s, kx + x * 64, krow);
+#pragma unroll
+                for (int x = BOXES_OWN; x < BOXES_K; ++x) tma_load_2d(kd + x * 8192, &tail_map, full + s, a.tail_col0 + (x - BOXES_OWN) * 64, krow);
+#pragma unroll
+                for (int x = 0; x < BOXES_V; ++x) tma_load_2d(kd + K_BYTES + x * 8192, &kv_map, full + s, vx + x * 64, vrow);
             }
         }
         return;
@@ -577,7 +583,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
     for (int i = 0; i < n_tiles; ++i) {
         const int s = i % STAGES;
         mbar_wait(full + s, (i / STAGES) & 1, &g_attn_error, 5);
-        const uint32_t ks_base = smem_u32(base + s * 2 * TILE_BYTES), vs_base = ks_base + TILE_BYTES;
+        const uint32_t ks_base = smem_u32(base + s * STAGE_BYTES), vs_base = ks_base + K_BYTES;
         float sc[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
@@ -641,8 +647,8 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
-    __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qr0) * a.out_stride + h * HD + 2 * t;
-    __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qr1) * a.out_stride + h * HD + 2 * t;
+    __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qr0) * a.out_stride + h * HDV + 2 * t;
+    __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qr1) * a.out_stride + h * HDV + 2 * t;
 #pragma unroll
     for (int nn = 0; nn < NT; ++nn) {
         if (qr0 < n) *reinterpret_cast<uint32_t*>(out0 + nn * 8) = pack2(o[nn][0] * i0, o[nn][1] * i0);
@@ -799,17 +805,17 @@ extern "C" int tb_attn_mma_error() {
     return (int)v;
 }
 
-template <int HD>
-static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, const PreArgs& p, dim3 grid, cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)(2 * 2 + 1) * 64 * HD * 2 + 8 * sizeof(uint64_t);
+template <int HDK, int HDV = HDK, int HDT = 0>
+static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, const CUtensorMap& tail_map, const PreArgs& p, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + (size_t)(2 * (HDK + HDV) + HDK) * 64 * 2 + 8 * sizeof(uint64_t);
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
+        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HDK, HDV, HDT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<HDK, HDV, HDT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "attn_prefill_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    tb_launch(attn_prefill_mma_kernel<HD>, grid, DEC_THREADS, smem, stream, map, kv_map, p);
+    tb_launch(attn_prefill_mma_kernel<HDK, HDV, HDT>, grid, DEC_THREADS, smem, stream, map, kv_map, tail_map, p);
     return 0;
 }
 
@@ -849,13 +855,61 @@ extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int source, cudaStream_
     p.v_row0 = a.cache.num_pages * a.nkv * PAGE;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
+    p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd; p.tail_col0 = 0;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
     TB_REQUIRE(blocks <= 65535, "attn_prefill_mma: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);
-    const int rc = a.hd == 128 ? launch_prefill<128>(map, kv_map, p, grid, stream) : launch_prefill<64>(map, kv_map, p, grid, stream);
+    const int rc = a.hd == 128 ? launch_prefill<128>(map, kv_map, kv_map, p, grid, stream) : launch_prefill<64>(map, kv_map, kv_map, p, grid, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("attn_prefill_mma");
+    return 0;
+}
+
+// Prompts whose sequences all start at position 0, with keys in two parts and values of another width than keys:
+//   query of head h   q[t][h * (dn + dt) ..]                      [own part dn | shared part dt]
+//   key of head h     kv[t][k_col0 + h * dn ..] | tail[t][tail_col0 ..]   (the second part is one for all heads)
+//   value of head h   kv[t][v_col0 + h * dv ..];   out[t][h * dv ..]
+// which is what attention over a shared latent looks like once keys and values are expanded per head.  Built for
+// dn = 128, dt = 64, dv = 128 (the check says no to other sizes, and the caller takes another kernel).
+struct SplitAttnArgs {
+    const void* q; int q_stride;
+    const void* kv; int kv_stride; int k_col0; int v_col0;
+    const void* tail; int tail_stride; int tail_col0;
+    void* out; int out_stride;
+    TbBatch batch;
+    int nh; int dn; int dt; int dv; int window; float scale;
+};
+
+extern "C" int tb_attn_prefill_split_check(const SplitAttnArgs* a) {
+    TB_REQUIRE(a->dn == 128 && a->dt == 64 && a->dv == 128, "attn_prefill_split: built for keys of 128 + 64 and values of 128, not %d + %d and %d", a->dn, a->dt, a->dv);
+    TB_REQUIRE(a->q && a->kv && a->tail && a->out && a->nh > 0, "attn_prefill_split: missing buffers");
+    TB_REQUIRE(a->q_stride % 8 == 0 && a->kv_stride % 8 == 0 && a->tail_stride % 8 == 0 && a->k_col0 % 8 == 0 && a->v_col0 % 8 == 0 && a->tail_col0 % 8 == 0,
+               "attn_prefill_split: rows and first columns must be multiples of 8 elements (16-byte TMA coordinates)");
+    TB_REQUIRE((((uintptr_t)a->q | (uintptr_t)a->kv | (uintptr_t)a->tail) & 15) == 0, "attn_prefill_split: buffers must be 16-byte aligned");
+    TB_REQUIRE(a->out_stride % 2 == 0 && ((uintptr_t)a->out & 3) == 0, "attn_prefill_split: the output must be 4-byte aligned");
+    TB_REQUIRE(a->window >= 0, "attn_prefill_split: negative window");
+    return 0;
+}
+
+extern "C" int tb_attn_prefill_split(const SplitAttnArgs* args, cudaStream_t stream) {
+    const SplitAttnArgs& a = *args;
+    if (tb_attn_prefill_split_check(args)) return 1;
+    TB_REQUIRE(a.batch.T > 0 && a.batch.B > 0, "attn_prefill_split: no tokens");
+    CUtensorMap q_map, kv_map, tail_map;
+    if (tb_make_map_bf16(&q_map, a.q, a.batch.T, a.q_stride, a.q_stride, 64)) return 1;
+    if (tb_make_map_bf16(&kv_map, a.kv, a.batch.T, a.kv_stride, a.kv_stride, 64)) return 1;
+    if (tb_make_map_bf16(&tail_map, a.tail, a.batch.T, a.tail_stride, a.tail_stride, 64)) return 1;
+    PreArgs p;
+    p.paged = 0; p.start_pos = nullptr; p.slot_of_seq = nullptr; p.table = nullptr; p.table_width = 0; p.v_row0 = 0;
+    p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
+    p.nh = a.nh; p.nkv = a.nh; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.k_col0 = a.k_col0; p.v_col0 = a.v_col0; p.tail_col0 = a.tail_col0;
+    const int blocks = (a.batch.T + 63) / 64 + a.batch.B;
+    TB_REQUIRE(blocks <= 65535, "attn_prefill_split: too many query blocks (%d)", blocks);
+    dim3 grid(a.nh, blocks);
+    const int rc = launch_prefill<192, 128, 64>(q_map, kv_map, tail_map, p, grid, stream);
+    if (rc) return rc;
+    TB_CHECK_LAUNCH("attn_prefill_split");
     return 0;
 }
 

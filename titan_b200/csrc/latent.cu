@@ -28,6 +28,7 @@ struct LatentArgs {
     int owner;                              // the projection row holds a latent and a key part
     const int* pos_of; const int* seq_of; const int* slot_of_seq; const int* kv_len;
     TbKvView cache; int append; int T;
+    void* q_full; int qf_stride;            // if set: [T][qf_stride], head h at h * (dn + rd) as [unrotated dn | rotated rd]; q_nope and q_abs are not written
 };
 
 namespace {
@@ -62,16 +63,24 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(LatentArgs a) {
     }
     __syncthreads();
     const int qw = a.dn + a.rd;
-    T* qn = (T*)a.q_nope + (size_t)t * a.qn_stride;
-    T* qa = (T*)a.q_abs + (size_t)t * a.qa_stride;
-    for (int i = threadIdx.x; i < a.H * a.dn; i += blockDim.x) {
-        const int h = i / a.dn, d = i % a.dn;
-        stf(qn + i, row[h * qw + d]);
-    }
-    const int tail = a.dk - a.r;            // rotated part and padding
-    for (int i = threadIdx.x; i < a.H * tail; i += blockDim.x) {
-        const int h = i / tail, e = i % tail;
-        stf(qa + (size_t)h * a.dk + a.r + e, e < a.rd ? rotated(row + h * qw + a.dn, e, a.rope, cs, sn) : 0.f);
+    if (a.q_full) {                          // whole heads for a kernel that scores expanded keys: [unrotated | rotated]
+        T* qf = (T*)a.q_full + (size_t)t * a.qf_stride;
+        for (int i = threadIdx.x; i < a.H * qw; i += blockDim.x) {
+            const int h = i / qw, d = i % qw;
+            stf(qf + i, d < a.dn ? row[i] : rotated(row + h * qw + a.dn, d - a.dn, a.rope, cs, sn));
+        }
+    } else {
+        T* qn = (T*)a.q_nope + (size_t)t * a.qn_stride;
+        T* qa = (T*)a.q_abs + (size_t)t * a.qa_stride;
+        for (int i = threadIdx.x; i < a.H * a.dn; i += blockDim.x) {
+            const int h = i / a.dn, d = i % a.dn;
+            stf(qn + i, row[h * qw + d]);
+        }
+        const int tail = a.dk - a.r;        // rotated part and padding
+        for (int i = threadIdx.x; i < a.H * tail; i += blockDim.x) {
+            const int h = i / tail, e = i % tail;
+            stf(qa + (size_t)h * a.dk + a.r + e, e < a.rd ? rotated(row + h * qw + a.dn, e, a.rope, cs, sn) : 0.f);
+        }
     }
     if (!a.owner) return;
     const float* lat = row + a.H * qw;
@@ -114,7 +123,7 @@ extern "C" int tb_latent_prep(const LatentArgs* args, int out_dtype, cudaStream_
     TB_REQUIRE(a.T > 0 && a.H > 0 && a.dn > 0 && a.rd >= 0 && a.r > 0, "latent_prep: sizes must be positive");
     TB_REQUIRE(a.dk >= a.r + a.rd && a.dk % 8 == 0, "latent_prep: a row of %d elements for %d + %d (a multiple of 8 that holds both)", a.dk, a.r, a.rd);
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot % 2 == 0 && a.rope.rot <= a.rd, "latent_prep: %d rotated dimensions of %d", a.rope.rot, a.rd);
-    TB_REQUIRE(a.in && a.q_nope && a.q_abs, "latent_prep: missing buffers");
+    TB_REQUIRE(a.in && (a.q_full || (a.q_nope && a.q_abs)), "latent_prep: missing buffers");
     TB_REQUIRE(a.in_stride >= a.H * (a.dn + a.rd) + (a.owner ? a.r + a.rd : 0), "latent_prep: the projection row is too short");
     TB_REQUIRE(!a.owner || a.latent_w, "latent_prep: the latent's norm weight is missing");
     TB_REQUIRE(!a.append || (a.owner && a.cache.storage && a.cache.head_dim == a.dk && a.cache.kv_heads == 1), "latent_prep: the cache view does not match the rows");

@@ -23,6 +23,19 @@
 
 namespace {
 
+// 16 bytes of a row as floats: 4 float32 or 8 bfloat16.
+template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* o);
+template <> __device__ __forceinline__ void load_vec<float>(const float* p, float* o) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+}
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+
 // ------------------------------------------------------------------ route
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int has_gate,
                                                         int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int T_) {
@@ -65,7 +78,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 // counts [E], rank [P] are scratch; perm [P]; tiles: tile_e, tile_row0, tile_rows [max_tiles]; n_tiles [1].
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ rank,
                                                         int* __restrict__ perm, int* __restrict__ tile_e, int* __restrict__ tile_row0,
-                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles, int max_tiles) {
+                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles, int max_tiles,
+                                                        int* __restrict__ offsets, int* __restrict__ inverse) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ int smi[];            // count [E], offset [E]
@@ -88,7 +102,28 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
         *n_tiles = min(tiles, max_tiles);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < P; i += blockDim.x) perm[offset[ids[i]] + rank[i]] = i;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = e < E ? offset[e] : P;     // first sorted row of every expert, then P
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+        const int at = offset[ids[i]] + rank[i];
+        perm[at] = i;
+        inverse[i] = at;
+    }
+}
+
+// out[r] = x[perm[r] / top]: the tokens' rows in the plan's order, for products that want an expert's rows side by side.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ perm, int top, T* __restrict__ out, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    const T* src = x + (size_t)(perm[r] / top) * ldx;
+    T* dst = out + r * K;
+    constexpr int PER = 16 / sizeof(T);
+    if (K % PER == 0 && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0)) {
+        for (int e = threadIdx.x; e < K / PER; e += blockDim.x) reinterpret_cast<uint4*>(dst)[e] = reinterpret_cast<const uint4*>(src)[e];
+    } else {
+        for (int e = threadIdx.x; e < K; e += blockDim.x) dst[e] = src[e];
+    }
 }
 
 // ------------------------------------------------------------------ grouped product on the CUDA cores
@@ -186,10 +221,20 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
     if (n >= N_out) return;
     const int e = ids[p];
     const T* x = X + (size_t)(MODE == 0 ? p / top : p) * ldx;
+    constexpr int PER = 16 / sizeof(T);                 // elements of a 16-byte load
+    const bool wide = K % PER == 0 && ldx % PER == 0 && ((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0);
     if (MODE == 0) {
         const T* wg = W + ((size_t)e * 2 * N_out + 2 * n) * K;
         const T* wu = wg + K;
         float g = 0.f, u = 0.f;
+        if (wide) {
+            for (int k = lane * PER; k < K; k += 32 * PER) {
+                float xv[PER], a[PER], b[PER];
+                load_vec<T>(x + k, xv); load_vec<T>(wg + k, a); load_vec<T>(wu + k, b);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) { g = fmaf(a[i], xv[i], g); u = fmaf(b[i], xv[i], u); }
+            }
+        } else
         for (int k = lane; k < K; k += 32) {
             const float xv = ldf(x + k);
             g = fmaf(ldf(wg + k), xv, g);
@@ -200,6 +245,14 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
     } else {
         const T* w = W + ((size_t)e * N_out + n) * K;
         float s = 0.f;
+        if (wide) {
+            for (int k = lane * PER; k < K; k += 32 * PER) {
+                float xv[PER], a[PER];
+                load_vec<T>(x + k, xv); load_vec<T>(w + k, a);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) s = fmaf(a[i], xv[i], s);
+            }
+        } else
         for (int k = lane; k < K; k += 32) s = fmaf(ldf(w + k), ldf(x + k), s);
         s = warp_sum(s);
         if (lane == 0) ((float*)out)[(size_t)p * ldo + n] = s;
@@ -208,13 +261,16 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
 
 // ------------------------------------------------------------------ combine
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, const float* __restrict__ shared_y,
-                                   const float* __restrict__ gate, float* __restrict__ out, int H, int top) {
+                                   const float* __restrict__ gate, float* __restrict__ out, int H, int top, const int* __restrict__ where) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(wts[t * top + k], y[(t * top + k) * H + i], s);
+        for (int k = 0; k < top; ++k) {
+            const size_t row = where ? (size_t)where[t * top + k] : t * top + k;       // pair order, or where the plan put the pair
+            s = fmaf(wts[t * top + k], y[row * H + i], s);
+        }
         if (shared_y) s = fmaf(gate ? gate[t] : 1.f, shared_y[t * H + i], s);
         out[t * H + i] += s;
     }
@@ -235,10 +291,10 @@ extern "C" int tb_moe_route(const float* z, int ldz, int E, int top, int has_gat
 extern "C" int tb_moe_plan_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
 
 extern "C" int tb_moe_plan(const int* ids, int P, int E, int* rank, int* perm, int* tile_e, int* tile_row0, int* tile_rows,
-                           int* n_tiles, int max_tiles, cudaStream_t stream) {
+                           int* n_tiles, int max_tiles, int* offsets, int* inverse, cudaStream_t stream) {
     TB_REQUIRE(P > 0 && E > 0 && E <= 4096, "moe_plan: %d pairs, %d experts (at most 4096)", P, E);
     TB_REQUIRE(max_tiles >= tb_moe_plan_tiles(P, E), "moe_plan: room for %d tiles, %d may be needed", max_tiles, tb_moe_plan_tiles(P, E));
-    tb_launch(moe_plan_kernel, 1, 1024, (size_t)2 * E * sizeof(int), stream, ids, P, E, rank, perm, tile_e, tile_row0, tile_rows, n_tiles, max_tiles);
+    tb_launch(moe_plan_kernel, 1, 1024, (size_t)2 * E * sizeof(int), stream, ids, P, E, rank, perm, tile_e, tile_row0, tile_rows, n_tiles, max_tiles, offsets, inverse);
     TB_CHECK_LAUNCH("moe_plan");
     return 0;
 }
@@ -273,10 +329,20 @@ extern "C" int tb_moe_rows(const void* X, int ldx, const void* W, void* out, int
     return 0;
 }
 
+extern "C" int tb_moe_gather(const void* x, int ldx, const int* perm, int top, void* out, int dtype, int P, int K, cudaStream_t stream) {
+    TB_REQUIRE(P > 0 && K > 0 && top > 0 && x && perm && out, "moe_gather: sizes must be positive");
+    if (dtype == TB_F32) tb_launch(moe_gather_kernel<float>, P, 128, 0, stream, (const float*)x, ldx, perm, top, (float*)out, K);
+    else if (dtype == TB_BF16) tb_launch(moe_gather_kernel<__nv_bfloat16>, P, 128, 0, stream, (const __nv_bfloat16*)x, ldx, perm, top, (__nv_bfloat16*)out, K);
+    else TB_REQUIRE(false, "moe_gather: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("moe_gather");
+    return 0;
+}
+
+// ``where`` (may be null): row of y that holds pair p, if y is not in pair order.
 extern "C" int tb_moe_combine(const float* y, const float* wts, const float* shared_y, const float* gate, float* out, int T_,
-                              int H, int top, cudaStream_t stream) {
+                              int H, int top, const int* where, cudaStream_t stream) {
     TB_REQUIRE(T_ > 0 && H > 0 && top > 0 && y && wts && out, "moe_combine: sizes must be positive");
-    tb_launch(moe_combine_kernel, T_, H >= 1024 ? 256 : 128, 0, stream, y, wts, shared_y, gate, out, H, top);
+    tb_launch(moe_combine_kernel, T_, H >= 1024 ? 256 : 128, 0, stream, y, wts, shared_y, gate, out, H, top, where);
     TB_CHECK_LAUNCH("moe_combine");
     return 0;
 }

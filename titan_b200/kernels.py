@@ -82,7 +82,7 @@ class AttnArgs(Structure):
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
                 ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs)),
-                ("hd_v", c_int), ("v_alias", c_int)]
+                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int)]
 
 
 class LatentArgs(Structure):
@@ -92,7 +92,14 @@ class LatentArgs(Structure):
                 ("latent_w", c_void_p), ("eps", c_float), ("rope", RotaryArgs),
                 ("H", c_int), ("dn", c_int), ("rd", c_int), ("r", c_int), ("dk", c_int), ("owner", c_int),
                 ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p), ("kv_len", c_void_p),
-                ("cache", KvView), ("append", c_int), ("T", c_int)]
+                ("cache", KvView), ("append", c_int), ("T", c_int), ("q_full", c_void_p), ("qf_stride", c_int)]
+
+
+class SplitAttnArgs(Structure):
+    """Arguments of the tensor-core prompt attention with keys in two parts (csrc/attention_mma.cu: tb_attn_prefill_split)."""
+    _fields_ = [("q", c_void_p), ("q_stride", c_int), ("kv", c_void_p), ("kv_stride", c_int), ("k_col0", c_int), ("v_col0", c_int),
+                ("tail", c_void_p), ("tail_stride", c_int), ("tail_col0", c_int), ("out", c_void_p), ("out_stride", c_int),
+                ("batch", Batch), ("nh", c_int), ("dn", c_int), ("dt", c_int), ("dv", c_int), ("window", c_int), ("scale", c_float)]
 
 
 class LightningArgs(Structure):
@@ -137,11 +144,12 @@ def lib():
         l.tb_gated_rmsnorm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]
         l.tb_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_moe_plan_tiles.argtypes = [c_int, c_int]
-        l.tb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        l.tb_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_moe_grouped.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_moe_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        l.tb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
@@ -171,6 +179,8 @@ def tlib():
         l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
         l.tb_attn_prefill_mma.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_mma_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
+        l.tb_attn_prefill_split.argtypes = [POINTER(SplitAttnArgs), c_void_p]
+        l.tb_attn_prefill_split_check.argtypes = [POINTER(SplitAttnArgs)]
         l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
         _tlib = l
@@ -331,29 +341,53 @@ def moe_plan_tiles(pairs: int, experts: int) -> int:
     return int(lib().tb_moe_plan_tiles(pairs, experts))
 
 
-def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor, stream: int):
-    """Groups the (token, choice) pairs by expert.  ``plan`` is int32 scratch of at least 2 P + 3 tiles + 1; returns the
-    views (perm, tile_e, tile_row0, tile_rows, n_tiles, max_tiles) the grouped product takes."""
-    P = ids.numel()
-    tiles = moe_plan_tiles(P, experts)
-    if plan.numel() < 2 * P + 3 * tiles + 1:
-        raise KernelError("moe_plan: the plan's buffer is too small")
-    rank, perm = plan[:P], plan[P:2 * P]
-    te, tr0, trn = (plan[2 * P + i * tiles: 2 * P + (i + 1) * tiles] for i in range(3))
-    n = plan[2 * P + 3 * tiles: 2 * P + 3 * tiles + 1]
-    _check(lib().tb_moe_plan(ids.data_ptr(), P, experts, rank.data_ptr(), perm.data_ptr(), te.data_ptr(), tr0.data_ptr(),
-                             trn.data_ptr(), n.data_ptr(), tiles, stream))
-    return perm, te, tr0, trn, n, tiles
+class MoePlan:
+    """The (token, choice) pairs grouped by expert, as views of one int32 buffer: ``perm`` sorted row -> pair, ``inverse``
+    pair -> sorted row, ``offsets`` [E + 1] first sorted row of every expert, and the row tiles of the grouped product."""
+
+    def __init__(self, buffer: torch.Tensor, pairs: int, experts: int):
+        P, tiles = pairs, moe_plan_tiles(pairs, experts)
+        if buffer.numel() < self.size(pairs, experts) or buffer.dtype != torch.int32:
+            raise KernelError("moe_plan: the plan's buffer is too small")
+        at = 0
+        def cut(n):
+            nonlocal at
+            at += n
+            return buffer[at - n: at]
+        self.rank, self.perm, self.inverse = cut(P), cut(P), cut(P)
+        self.tile_e, self.tile_row0, self.tile_rows = cut(tiles), cut(tiles), cut(tiles)
+        self.n_tiles, self.offsets = cut(1), cut(experts + 1)
+        self.tiles, self.pairs, self.experts = tiles, P, experts
+
+    @staticmethod
+    def size(pairs: int, experts: int) -> int:
+        return 3 * pairs + 3 * moe_plan_tiles(pairs, experts) + 1 + experts + 1
+
+
+def moe_plan(ids: torch.Tensor, experts: int, buffer: torch.Tensor, stream: int) -> MoePlan:
+    """Groups the (token, choice) pairs by expert into ``buffer`` (int32 scratch of MoePlan.size elements)."""
+    plan = MoePlan(buffer, ids.numel(), experts)
+    _check(lib().tb_moe_plan(ids.data_ptr(), plan.pairs, experts, plan.rank.data_ptr(), plan.perm.data_ptr(), plan.tile_e.data_ptr(),
+                             plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(), plan.n_tiles.data_ptr(), plan.tiles,
+                             plan.offsets.data_ptr(), plan.inverse.data_ptr(), stream))
+    return plan
+
+
+def moe_gather(x: torch.Tensor, plan: MoePlan, top: int, out: torch.Tensor, stream: int) -> None:
+    """out[r] = x[plan.perm[r] // top]: the tokens' rows in the plan's order (out [P, K] contiguous, x's dtype)."""
+    _need_cuda(x, out)
+    if out.dtype != x.dtype or not out.is_contiguous() or x.stride(1) != 1 or out.shape != (plan.pairs, x.shape[1]):
+        raise KernelError("moe_gather: a contiguous [pairs, K] output of the input's dtype is wanted")
+    _check(lib().tb_moe_gather(x.data_ptr(), x.stride(0), plan.perm.data_ptr(), top, out.data_ptr(), dtype_code(x.dtype), plan.pairs, x.shape[1], stream))
 
 
 def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, plan, top: int, stream: int) -> None:
     """The experts' products over the plan's tiles on the CUDA cores.  mode 0: x [T, K] tokens, w [E, 2F, K] (gate and up
     rows interleaved), out [P, F] in sorted order; mode 1: x [P, K] sorted rows, w [E, N, K], out float32 [P, N] in pair order."""
     _need_cuda(x, w, out)
-    perm, te, tr0, trn, n, tiles = plan
     _check(lib().tb_moe_grouped(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), dtype_code(w.dtype), mode,
-                                perm.data_ptr(), te.data_ptr(), tr0.data_ptr(), trn.data_ptr(), n.data_ptr(), tiles,
-                                w.shape[1], w.shape[2], top, stream))
+                                plan.perm.data_ptr(), plan.tile_e.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(),
+                                plan.n_tiles.data_ptr(), plan.tiles, w.shape[1], w.shape[2], top, stream))
 
 
 def moe_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ids: torch.Tensor, top: int, stream: int) -> None:
@@ -365,10 +399,12 @@ def moe_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ids
 
 
 def moe_combine(y: torch.Tensor, wts: torch.Tensor, shared_y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-                out: torch.Tensor, top: int, stream: int) -> None:
-    """out[t] += sum_k wts[t, k] * y[t * top + k] (+ gate[t] * shared_y[t]); everything float32."""
-    _need_cuda(y, wts, shared_y, gate, out)
-    _check(lib().tb_moe_combine(y.data_ptr(), wts.data_ptr(), _ptr(shared_y), _ptr(gate), out.data_ptr(), out.shape[0], out.shape[1], top, stream))
+                out: torch.Tensor, top: int, stream: int, where: Optional[torch.Tensor] = None) -> None:
+    """out[t] += sum_k wts[t, k] * y[row of pair t * top + k] (+ gate[t] * shared_y[t]); everything float32.  The row of
+    pair p is p, or ``where[p]`` if y is in another order (a plan's ``inverse``)."""
+    _need_cuda(y, wts, shared_y, gate, out, where)
+    _check(lib().tb_moe_combine(y.data_ptr(), wts.data_ptr(), _ptr(shared_y), _ptr(gate), out.data_ptr(), out.shape[0], out.shape[1], top,
+                                _ptr(where), stream))
 
 
 def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> bool:
@@ -486,6 +522,16 @@ def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, source: int) ->
 def attn_prefill_mma(args: AttnArgs, source: int, stream: int) -> None:
     """Causal attention of prompts and continuation chunks on tensor cores (bfloat16, head_dim 64 or 128)."""
     _check(tlib().tb_attn_prefill_mma(byref(args), int(source), stream))
+
+
+def attn_prefill_split_accepts(args: "SplitAttnArgs") -> bool:
+    return tlib().tb_attn_prefill_split_check(byref(args)) == 0
+
+
+def attn_prefill_split(args: "SplitAttnArgs", stream: int) -> None:
+    """Causal (windowed) attention of prompts that start at position 0 on tensor cores, a key being [a part of its own head |
+    a part all heads share] and values of their own width (bfloat16; keys of 128 + 64, values of 128)."""
+    _check(tlib().tb_attn_prefill_split(byref(args), stream))
 
 
 def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, source: int) -> bool:

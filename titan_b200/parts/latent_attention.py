@@ -93,8 +93,11 @@ class LatentAttentionMixer(Mixer):
             norm.bind(lambda name: get(p + name))
             self.latent_w = norm.weight
         # U_k by head, transposed: [H, kv_rank, dim], so that q~_h = q_h . (that)^T; U_v by head as stored: [H, vdim, kv_rank]
-        self.w_uk_t = get(p + n["uk"]).view(self.H, self.dn, self.r).transpose(1, 2).contiguous()
-        self.w_uv = get(p + n["uv"]).view(self.H, self.dv, self.r).contiguous()
+        uk, uv = get(p + n["uk"]), get(p + n["uv"])
+        self.w_uk_t = uk.view(self.H, self.dn, self.r).transpose(1, 2).contiguous()
+        self.w_uv = uv.view(self.H, self.dv, self.r).contiguous()
+        # both expansions as one matrix, for prompts that expand keys and values per head (see _expanded_prompt)
+        self.w_ukv = torch.cat([uk, uv], dim=0).contiguous() if uk.dtype == torch.bfloat16 else None
         self.w_o = get(p + n["o"])
 
     # -- one step --------------------------------------------------------- #
@@ -108,6 +111,23 @@ class LatentAttentionMixer(Mixer):
                                         group.ring_rows, group.page_size, group.num_pages, 1, self.dk)
         return self._views[key]
 
+    def _split_args(self, ctx, q_full, kv, rows, o):
+        """Arguments of the tensor-core prompt kernel that scores expanded keys (or None where it does not apply)."""
+        s, lay = self.spec, ctx.layout
+        if (self.w_ukv is None or not lay.all_fresh or lay.all_single or ctx.options.get("attention", "fast") == "plain"
+                or ctx.options.get("gemm", "fast") == "plain" or getattr(K, "attn_prefill_split", None) is None):
+            return None
+        a = K.SplitAttnArgs()
+        a.q, a.q_stride = (q_full.data_ptr(), q_full.stride(0)) if q_full is not None else (1 << 12, self.H * (self.dn + self.rd))
+        a.kv, a.kv_stride = (kv.data_ptr(), kv.stride(0)) if kv is not None else (1 << 12, self.w_ukv.shape[0])
+        a.k_col0, a.v_col0 = 0, self.H * self.dn
+        a.tail, a.tail_stride, a.tail_col0 = (rows.data_ptr() if rows is not None else 1 << 12), self.dk, self.r
+        a.out, a.out_stride = (o.data_ptr(), o.stride(0)) if o is not None else (1 << 12, self.H * self.dv)
+        a.batch = lay.c_struct()
+        a.nh, a.dn, a.dt, a.dv = self.H, self.dn, self.rd, self.dv
+        a.window, a.scale = s.window or 0, self.scale
+        return a if K.attn_prefill_split_accepts(a) else None
+
     def forward(self, h, ctx, cache, out: torch.Tensor) -> None:
         s, lay = self.spec, ctx.layout
         T, H, dn, rd, dv, r, dk = lay.T, self.H, self.dn, self.rd, self.dv, self.r, self.dk
@@ -116,7 +136,11 @@ class LatentAttentionMixer(Mixer):
         decode = lay.all_single
         proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear.matmul(h, self.w_in, proj, linear.EPI_F32, ctx)
-        q_nope, q_abs = ctx.empty((T, H * dn)), ctx.empty((T, H * dk))
+        # Whole prompts in bfloat16 with heads of the sizes the tensor-core kernel is built for: keys and values are
+        # expanded per head by one product (k_h = U_k,h c, v_h = U_v,h c) and scored as they are; no move into the latent space.
+        expanded = self._split_args(ctx, None, None, None, None) is not None
+        q_full = ctx.empty((T, H * (dn + rd))) if expanded else None
+        q_nope, q_abs = (None, None) if expanded else (ctx.empty((T, H * dn)), ctx.empty((T, H * dk)))
         rows = None
         rows_key = ("latent_rows", id(group), index)
         if not self.shared and not decode:
@@ -129,18 +153,28 @@ class LatentAttentionMixer(Mixer):
         append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
         la = K.LatentArgs()
         la.inp, la.in_stride = proj.data_ptr(), proj.stride(0)
-        la.q_nope, la.qn_stride = q_nope.data_ptr(), q_nope.stride(0)
-        la.q_abs, la.qa_stride = q_abs.data_ptr(), q_abs.stride(0)
+        if expanded:
+            la.q_full, la.qf_stride = q_full.data_ptr(), q_full.stride(0)
+        else:
+            la.q_nope, la.qn_stride = q_nope.data_ptr(), q_nope.stride(0)
+            la.q_abs, la.qa_stride = q_abs.data_ptr(), q_abs.stride(0)
         la.kv_rows, la.kv_stride = (None, 0) if (self.shared or rows is None) else (rows.data_ptr(), rows.stride(0))
         la.latent_w, la.eps = (None if self.shared else self.latent_w.data_ptr()), (0.0 if self.shared else self.latent_norm_spec.eps)
         la.rope = self.position.kernel_args(ctx.device)
         la.H, la.dn, la.rd, la.r, la.dk, la.owner = H, dn, rd, r, dk, int(not self.shared)
         la.pos_of, la.seq_of, la.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         la.kv_len, la.cache, la.append, la.T = lay.kv_len.data_ptr(), view, int(append_now), T
-        K.latent_prep(la, q_abs.dtype, ctx.stream)
+        K.latent_prep(la, ctx.dtype, ctx.stream)
         if not self.shared and not append_now:             # a ring, and sequences that go on: the rows wait until every reader has run
             batch = lay.c_struct()
             ctx.after_blocks.append(lambda: K.latent_append(rows, view, batch, ctx.stream))
+        if expanded:
+            kv = ctx.empty((T, self.w_ukv.shape[0]))
+            linear.matmul(rows[:, :r], self.w_ukv, kv, linear.EPI_STORE, ctx)
+            o = ctx.empty((T, H * dv))
+            K.attn_prefill_split(self._split_args(ctx, q_full, kv, rows, o), ctx.stream)
+            linear.matmul(o, self.w_o, out, linear.EPI_ADD, ctx)
+            return
         # the heads' unrotated queries into the latent space
         linear.matmul_heads(q_nope, self.w_uk_t, q_abs, H, dn, dk, ctx)
 
@@ -152,7 +186,10 @@ class LatentAttentionMixer(Mixer):
         aa.nh, aa.nkv, aa.hd, aa.hd_v, aa.v_alias = H, 1, dk, r, 1
         aa.window, aa.scale = s.window or 0, self.scale
         if decode:
-            chunk, splits = decode_split(lay, 1, ctx.options, False)
+            # all heads read one row per key: a block for every few heads (not one for the single "kv head"), and splits
+            # of one page, so that a window of some hundred keys still spreads over the machine
+            aa.head_blocks = H // 4 if H % 4 == 0 else (H // 2 if H % 2 == 0 else H)          # four heads (a warp each), two, or one a block
+            chunk, splits = decode_split(lay, 1, dict(ctx.options, attn_chunk=int(ctx.options.get("latent_chunk", 64))), False)
             need = lay.B * H * splits * (r + 2)
             scratch = ctx.scratch.get("attn_partials")
             if scratch is None or scratch.numel() < need:

@@ -9,7 +9,9 @@ interleaved at bind time ([E, 2F, H]) so that one product applies the activation
 Routing, grouping and the experts' products all happen on the device: nothing is read on the host, so decode steps
 are captured as graphs.  A step with few (token, choice) pairs runs a warp-per-output kernel that reads each chosen
 expert's rows once (a decode step is bound by those bytes); larger steps group the pairs by expert
-(``moe_plan``) and run tiles of rows of one expert each (``moe_grouped``).
+(``moe_plan``) and run tiles of rows of one expert each (``moe_grouped``, CUDA cores: float32, and decode steps of many
+sequences); a bfloat16 prompt gathers every expert's rows side by side and runs the tensor-core product expert by
+expert, reading the experts' row counts on the host.
 """
 from __future__ import annotations
 
@@ -81,7 +83,8 @@ class MixtureOfExperts(FeedForward):
         T, H, top, E = h.shape[0], self.spec.hidden_size, self.top, self.E
         P = T * top
         f32, i32 = torch.float32, torch.int32
-        z = ctx.empty((T, self.w_router.shape[0]), f32)
+        n_logits = self.w_router.shape[0]
+        z = ctx.empty((T, -(-n_logits // 4) * 4), f32)[:, :n_logits]       # rows of whole 16 bytes: the tensor-core product's output rule
         linear.matmul(h, self.w_router, z, linear.EPI_F32, ctx)
         ids, wts = ctx.empty((T, top), i32), ctx.empty((T, top), f32)
         gate = ctx.empty((T,), f32) if self.shared_F else None
@@ -96,11 +99,28 @@ class MixtureOfExperts(FeedForward):
         if P <= int(ctx.options.get("moe_rows_pairs", 64)):
             K.moe_rows(h, self.w_gate_up, act, 0, ids, top, ctx.stream)
             K.moe_rows(act, self.w_down, y, 1, ids, top, ctx.stream)
+            K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream)
+            return
+        plan = K.moe_plan(ids, E, ctx.empty((K.MoePlan.size(P, E),), i32), ctx.stream)
+        on_tensor_cores = (not ctx.layout.all_single and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
+                           and P >= int(ctx.options.get("moe_tensor_pairs", 512)))
+        if on_tensor_cores:
+            # A prompt: every expert's rows side by side, one tensor-core product per expert and matrix.  How many rows
+            # each expert got is read on the host (one small copy a layer); steps of single tokens never come here,
+            # so they stay free of host reads and are captured as graphs.
+            offsets = plan.offsets.tolist()
+            xs = ctx.empty((P, H))
+            K.moe_gather(h, plan, top, xs, ctx.stream)
+            for e in range(E):
+                a, b = offsets[e], offsets[e + 1]
+                if b > a:
+                    linear.matmul(xs[a:b], self.w_gate_up[e], act[a:b], linear.EPI_SWIGLU, ctx)
+                    linear.matmul(act[a:b], self.w_down[e], y[a:b], linear.EPI_F32, ctx)
+            K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream, where=plan.inverse)
         else:
-            plan = K.moe_plan(ids, E, ctx.empty((2 * P + 3 * K.moe_plan_tiles(P, E) + 1,), i32), ctx.stream)
             K.moe_grouped(h, self.w_gate_up, act, 0, plan, top, ctx.stream)
             K.moe_grouped(act, self.w_down, y, 1, plan, top, ctx.stream)
-        K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream)
+            K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream)
 
 
 FEED_FORWARDS.register("moe", MixtureOfExperts)

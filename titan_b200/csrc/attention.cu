@@ -5,7 +5,7 @@
 //                    written after attention)
 //   tb_attn_decode   one query per sequence over its cached keys, cut into splits by the sequence's
 //                    own length (tb_split_keys), each giving (max, sum, unnormalised output)
-//   tb_attn_merge    log-sum-exp merge of the chunks in chunk order
+//   tb_attn_merge    log-sum-exp merge of the chunks in chunk order (a block per sequence and head)
 //
 // One warp per (query, head): a lane scores one key per round with the whole query in shared
 // memory, the warp folds 32 scores into the running softmax, then every lane accumulates its
@@ -186,48 +186,43 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     }
 }
 
-// grid (B, nh), one warp: out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits in order.
-// Lane s holds the weight of split s (32 splits per round), so the loads of the accumulation are
-// independent of one another.
+// grid (B, nh), one block of up to 128 threads: out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits in
+// order.  Every thread finds the maximum and the weights' sum itself from the splits' (m, l) pairs (a few broadcast
+// loads) and adds up its own output dims, so the loads of different splits do not wait for one another; splits that saw
+// no key (all of them before a window's first key) are skipped.
 template <typename T, int MAXE>
 __global__ void attn_merge_kernel(AttnArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = value_width(a), stride = hd + 2;
+    const int b = blockIdx.x, h = blockIdx.y, hd = value_width(a), stride = hd + 2;
     const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
     const int len = a.batch.kv_len[b], keys = tb_split_keys(len, a.chunk, a.n_splits);
     const int used = min(a.n_splits, (len + keys - 1) / keys);
+    const int first = a.window > 0 ? max(0, len - a.window) / keys : 0;      // splits before the window's first key hold nothing
     float m = -FLT_MAX;
-    for (int s = lane; s < used; s += 32)
+    for (int s = first; s < used; ++s)
         if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
-    m = warp_max(m);
-    float l = 0.f, acc[MAXE];
+    constexpr int PER = (32 * MAXE + 127) / 128;
+    float l = 0.f, acc[PER];
 #pragma unroll
-    for (int j = 0; j < MAXE; ++j) acc[j] = 0.f;
-    for (int s0 = 0; s0 < used; s0 += 32) {
-        const int s = s0 + lane;
-        float w = 0.f;
-        if (s < used) {
-            const float ls = part[s * stride + hd + 1];
-            if (ls > 0.f) { w = expf(part[s * stride + hd] - m); l += w * ls; }
-        }
-        const int n = min(32, used - s0);
-        for (int k = 0; k < n; ++k) {
-            const float wk = __shfl_sync(0xffffffffu, w, k);
-            const float* p = part + (size_t)(s0 + k) * stride;
+    for (int j = 0; j < PER; ++j) acc[j] = 0.f;
+    for (int s = first; s < used; ++s) {
+        const float ls = part[s * stride + hd + 1];
+        if (!(ls > 0.f)) continue;
+        const float w = expf(part[s * stride + hd] - m);
+        l = fmaf(w, ls, l);
+        const float* p = part + (size_t)s * stride;
 #pragma unroll
-            for (int j = 0; j < MAXE; ++j) {
-                const int d = lane + 32 * j;
-                if (d < hd) acc[j] = fmaf(wk, p[d], acc[j]);
-            }
+        for (int j = 0; j < PER; ++j) {
+            const int d = threadIdx.x + blockDim.x * j;
+            if (d < hd) acc[j] = fmaf(w, p[d], acc[j]);
         }
     }
-    l = warp_sum(l);
     const float inv = 1.0f / l;
     T* o = (T*)a.out + (size_t)b * a.out_stride + h * hd;
 #pragma unroll
-    for (int j = 0; j < MAXE; ++j) {
-        const int d = lane + 32 * j;
+    for (int j = 0; j < PER; ++j) {
+        const int d = threadIdx.x + blockDim.x * j;
         if (d < hd) stf(o + d, acc[j] * inv);
     }
 }
@@ -276,7 +271,7 @@ extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t strea
     TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_merge: unknown dtype %d", dtype);
     dim3 mgrid(a.batch.B, a.nh);
     const bool wide = wide_rows(a);
-    ATT_DISPATCH(attn_merge_kernel, mgrid, 32, 0);
+    ATT_DISPATCH(attn_merge_kernel, mgrid, 128, 0);
     TB_CHECK_LAUNCH("attn_merge");
     return 0;
 }
@@ -294,7 +289,7 @@ extern "C" int tb_attn_decode(const AttnArgs* args, int dtype, cudaStream_t stre
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
     const bool wide = wide_rows(a);
     ATT_DISPATCH(attn_decode_kernel, grid, ATT_WARPS * 32, smem);
-    ATT_DISPATCH(attn_merge_kernel, mgrid, 32, 0);
+    ATT_DISPATCH(attn_merge_kernel, mgrid, 128, 0);
     TB_CHECK_LAUNCH("attn_decode");
     return 0;
 }

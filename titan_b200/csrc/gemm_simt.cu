@@ -107,6 +107,43 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx
     return 0;
 }
 
+// A few rows (decode steps): a warp per output element of one row and one product of the batch, lanes along K with
+// 16-byte loads where the rows allow; the weights are read once per row of X through L2.  STORE epilogue only.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict__ out, int M, int N, int K, int ldx, int ldo,
+                 long long sx, long long sw, long long so) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * 8 + warp, m = blockIdx.y, z = blockIdx.z;
+    if (n >= N) return;
+    const T* x = X + (size_t)z * sx + (size_t)m * ldx;
+    const T* w = W + (size_t)z * sw + (size_t)n * K;
+    constexpr int PER = 16 / sizeof(T);
+    float acc = 0.f;
+    if (K % PER == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) {
+        for (int k = lane * PER; k < K; k += 32 * PER) {
+            if (sizeof(T) == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(x + k), b = *reinterpret_cast<const float4*>(w + k);
+                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+            } else {
+                const uint4 a = *reinterpret_cast<const uint4*>(x + k), b = *reinterpret_cast<const uint4*>(w + k);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), acc);
+                    acc = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), acc);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(ldf(x + k), ldf(w + k), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) stf(out + (size_t)z * so + (size_t)m * ldo + n, acc);
+}
+
 }  // namespace
 
 // ldx: row stride of X in elements; ldo: row stride of out in elements.  ``batch`` products of the same shape in one
@@ -118,6 +155,14 @@ extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int
     TB_REQUIRE(ldx >= K, "gemm: row stride %d of X is shorter than K=%d", ldx, K);
     TB_REQUIRE(epi != TB_EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N, found %d", N);
     TB_REQUIRE((M + BM - 1) / BM <= 65535, "gemm: M=%d is too large for one launch", M);
+    if (epi == TB_EPI_STORE && M <= 16 && batch > 1 && (N + 7) / 8 <= 65535) {      // a decode step's rows: a warp per output
+        dim3 grid((N + 7) / 8, M, batch);
+        if (dtype == TB_F32) tb_launch(gemm_rows_kernel<float>, grid, 256, 0, stream, (const float*)X, (const float*)W, (float*)out, M, N, K, ldx, ldo, sx, sw, so);
+        else if (dtype == TB_BF16) tb_launch(gemm_rows_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, M, N, K, ldx, ldo, sx, sw, so);
+        else { tb_set_error("gemm: unknown dtype %d", dtype); return 1; }
+        TB_CHECK_LAUNCH("gemm_rows");
+        return 0;
+    }
     int rc;
     if (dtype == TB_F32) rc = launch<float>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
     else if (dtype == TB_BF16) rc = launch<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);

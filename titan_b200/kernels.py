@@ -106,7 +106,7 @@ class LightningArgs(Structure):
     """Arguments of the decayed linear-attention recurrence (csrc/lightning.cu)."""
     _fields_ = [("proj", c_void_p), ("stride", c_int), ("out", c_void_p), ("out_stride", c_int), ("state", c_void_p),
                 ("decay", c_void_p), ("q_start", c_void_p), ("slot_of_seq", c_void_p),
-                ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int)]
+                ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int), ("max_new", c_int)]
 
 
 class SampleArgs(Structure):

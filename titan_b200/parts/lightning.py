@@ -75,7 +75,7 @@ class LightningMixer(Mixer):
         a.out, a.out_stride = o.data_ptr(), o.stride(0)
         a.state, a.decay = group.layer_storage(index).data_ptr(), self.decay.data_ptr()
         a.q_start, a.slot_of_seq = lay.q_start.data_ptr(), lay.slot_of_seq.data_ptr()
-        a.B, a.H, a.dk, a.dv = lay.B, H, dk, dv
+        a.B, a.H, a.dk, a.dv, a.max_new = lay.B, H, dk, dv, lay.max_new
         K.lightning_scan(a, proj.dtype, ctx.stream)
         y = ctx.empty((T, H * dv))
         K.gated_rmsnorm(o, self.norm_w, proj[:, 2 * H * dk + H * dv:], y, self.out_norm_spec.eps, ctx.stream)

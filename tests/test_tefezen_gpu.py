@@ -188,7 +188,8 @@ def test_latent_attention_alone(dtype, H, dn, rd, dv, r, window, rot_dims):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,dk,dv,decay", [(3, 8, 16, [0.3, 0.9, 1.0]), (1, 40, 33, [0.999]), (2, 130, 70, [0.95, 0.99])])
+@pytest.mark.parametrize("H,dk,dv,decay", [(3, 8, 16, [0.3, 0.9, 1.0]), (1, 40, 33, [0.999]), (2, 130, 70, [0.95, 0.99]),
+                                            (2, 64, 24, [0.9, 0.97]), (1, 136, 40, [0.99]), (1, 128, 128, [0.98])])     # the last three: sizes in multiples of 8, the kernel of 16-byte loads
 def test_lightning_alone(dtype, H, dk, dv, decay):
     """Two sequences through whole prompts, portions of two tokens and single tokens: outputs and the final state."""
     from titan_b200.cache import SequenceCache

@@ -1255,3 +1255,62 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
 
 // Names the buffer of the timeline probe (timeline.cuh); 1 if the library was built with it, 0 if not.
 TB_TIMELINE_SETTER(tb_gemm_tc_timeline)
+
+// Runs of rows of X, each with a matrix of its own: rows [first[s], first[s + 1]) of X times W + s * w_step (elements), into
+// the same rows of out; ``first`` (segments + 1 numbers, on the HOST) ascends.  One tb_gemm_tc per run that has rows,
+// issued from here so that the runs cost a launch each and no interpreter time (the experts of a mixture, whose rows a
+// prompt has gathered side by side).  The output's element size follows from the epilogue.
+extern "C" int tb_gemm_tc_segments(const void* X, int ldx, const void* W, long long w_step, void* out, int ldo, const int* first,
+                                   int segments, int N, int K, int epi, cudaStream_t stream) {
+    TB_REQUIRE(first && segments > 0, "gemm_tc_segments: no segments");
+    const size_t out_bytes = (epi == TB_EPI_STORE || epi == TB_EPI_SWIGLU) ? 2 : 4;
+    for (int s = 0; s < segments; ++s) {
+        const int a = first[s], M = first[s + 1] - a;
+        TB_REQUIRE(M >= 0, "gemm_tc_segments: the segments' first rows must ascend");
+        if (M == 0) continue;
+        const int rc = tb_gemm_tc((const char*)X + (size_t)a * ldx * 2, (const char*)W + (size_t)s * w_step * 2,
+                                  (char*)out + (size_t)a * ldo * out_bytes, M, N, K, ldx, ldo, epi, 0, stream);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+// The experts of a mixture over rows that a prompt has gathered side by side: for every run s of rows,
+//   act = swiglu(x . Wgu[s]^T)   then   y = act . Wd[s]^T   (float32),
+// two tensor-core products per run, the runs dealt round robin onto a few side streams so that several experts'
+// products, each too small to fill the machine, run beside one another.  The side streams start after what the
+// caller's stream has queued and the caller's stream goes on after all of them (events; no host wait).
+extern "C" int tb_gemm_tc_expert_runs(const void* X, int ldx, const void* Wgu, void* act, int ld_act, const void* Wd, void* y, int ldy,
+                                      const int* first, int runs, int H, int F, cudaStream_t stream) {
+    TB_REQUIRE(first && runs > 0 && H > 0 && F > 0, "gemm_tc_expert_runs: sizes must be positive");
+    constexpr int SIDE = 4;
+    static cudaStream_t side[SIDE];
+    static cudaEvent_t fork_ev, join_ev[SIDE];
+    static bool made = false;
+    if (!made) {
+        for (int i = 0; i < SIDE; ++i) {
+            TB_REQUIRE(cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking) == cudaSuccess, "gemm_tc_expert_runs: cannot create a stream");
+            TB_REQUIRE(cudaEventCreateWithFlags(&join_ev[i], cudaEventDisableTiming) == cudaSuccess, "gemm_tc_expert_runs: cannot create an event");
+        }
+        TB_REQUIRE(cudaEventCreateWithFlags(&fork_ev, cudaEventDisableTiming) == cudaSuccess, "gemm_tc_expert_runs: cannot create an event");
+        made = true;
+    }
+    cudaEventRecord(fork_ev, stream);
+    for (int i = 0; i < SIDE; ++i) cudaStreamWaitEvent(side[i], fork_ev, 0);
+    int rc = 0, used = 0;
+    for (int s = 0; s < runs && !rc; ++s) {
+        const int a = first[s], M = first[s + 1] - a;
+        if (M < 0) { tb_set_error("gemm_tc_expert_runs: the runs' first rows must ascend"); rc = 1; break; }
+        if (M == 0) continue;
+        cudaStream_t st = side[used++ % SIDE];
+        rc = tb_gemm_tc((const char*)X + (size_t)a * ldx * 2, (const char*)Wgu + (size_t)s * 2 * F * H * 2, (char*)act + (size_t)a * ld_act * 2,
+                        M, 2 * F, H, ldx, ld_act, TB_EPI_SWIGLU, 0, st);
+        if (!rc) rc = tb_gemm_tc((const char*)act + (size_t)a * ld_act * 2, (const char*)Wd + (size_t)s * H * F * 2, (char*)y + (size_t)a * ldy * 4,
+                                 M, H, F, ld_act, ldy, TB_EPI_F32, 0, st);
+    }
+    for (int i = 0; i < SIDE; ++i) {        // join in every case, also after a refusal: the caller's stream must not run ahead
+        cudaEventRecord(join_ev[i], side[i]);
+        cudaStreamWaitEvent(stream, join_ev[i], 0);
+    }
+    return rc;
+}

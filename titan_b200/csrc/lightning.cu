@@ -58,22 +58,29 @@ __global__ void __launch_bounds__(128) lightning_scan_kernel(LightningArgs a) {
     const T* base = (const T*)a.proj;
     const int kq = h * dk, kk = a.H * dk + h * dk, kvv = 2 * a.H * dk + h * dv + blockIdx.z * 32;
     float stage[PER];
-    // element e of a chunk's staging area: token e / ROW, and within the row q (padded), k (padded) or a value
+    // Element e of a chunk's staging area: token e / ROW, and within the row q (padded), k (padded) or a value.  Gives
+    // the address to read (always a valid one: indices are clamped, so that the load needs no condition and nothing
+    // waits for it before the chunk is due) and whether the element is real or padding.
+    auto source = [&](int u, int first, bool* real) -> const T* {
+        const int e = tid + 128 * u, ec = min(e, CH * ROW - 1), tok = ec / ROW, x = ec % ROW;
+        bool ok = e < CH * ROW && first + tok < t1;
+        const T* row = base + (size_t)min(first + tok, t1 - 1) * a.stride;
+        if (x < 2 * DKP) {
+            const int y = x < DKP ? x : x - DKP, run = y / (R + 4), within = y % (R + 4), i = run * R + within;
+            ok = ok && within < R && i < dk;
+            *real = ok;
+            return row + (x < DKP ? kq : kk) + (ok ? i : 0);
+        }
+        const int c = x - 2 * DKP;
+        ok = ok && blockIdx.z * 32 + c < dv;
+        *real = ok;
+        return row + kvv + (ok ? c : 0);
+    };
     auto request = [&](int first) {
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
-            const int e = tid + 128 * u, tok = e / ROW, x = e % ROW;
-            float v = 0.f;
-            if (e < CH * ROW && first + tok < t1) {
-                const T* row = base + (size_t)(first + tok) * a.stride;
-                if (x < 2 * DKP) {
-                    const int y = x < DKP ? x : x - DKP, run = y / (R + 4), within = y % (R + 4), i = run * R + within;
-                    if (within < R && i < dk) v = ldf(row + (x < DKP ? kq : kk) + i);
-                } else if (blockIdx.z * 32 + (x - 2 * DKP) < dv) {
-                    v = ldf(row + kvv + (x - 2 * DKP));
-                }
-            }
-            stage[u] = v;
+            bool real;
+            stage[u] = ldf(source(u, first, &real));
         }
     };
     if (t0 < t1) request(t0);
@@ -82,7 +89,9 @@ __global__ void __launch_bounds__(128) lightning_scan_kernel(LightningArgs a) {
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
             const int e = tid + 128 * u;
-            if (e < CH * ROW) sm[e] = silu_f(stage[u]);   // silu(0) = 0: the padding stays zero
+            bool real;
+            source(u, c0, &real);
+            if (e < CH * ROW) sm[e] = real ? silu_f(stage[u]) : 0.f;
         }
         __syncthreads();
         if (c0 + CH < t1) request(c0 + CH);
@@ -102,6 +111,126 @@ __global__ void __launch_bounds__(128) lightning_scan_kernel(LightningArgs a) {
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + h * dv + j] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < R; ++ii) {
+            const int i = s * R + ii;
+            if (i < dk) S_g[(size_t)i * dv] = S[ii];
+        }
+    }
+}
+
+// Eight consecutive elements of a row, as they come from one (bfloat16) or two (float32) 16-byte loads.
+template <typename T> struct Pack8;
+template <> struct Pack8<__nv_bfloat16> {
+    uint4 a;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void get(float* o) const {
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+};
+template <> struct Pack8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *reinterpret_cast<const float4*>(p); b = *reinterpret_cast<const float4*>(p + 4); }
+    __device__ __forceinline__ void get(float* o) const { o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w; }
+};
+
+// The same recurrence for sizes in multiples of 8 (dk, dv, the projection's row stride): a block owns 16 value columns,
+// eight neighbouring lanes share a column (R rows of it each, dk <= 8 R), and a chunk of tokens is staged by 16-byte
+// loads of eight elements, a few a thread.  Twice the blocks of the kernel above, half the arithmetic a thread and
+// token, and an eighth of the load instructions.
+template <typename T, int R, int CH>
+__global__ void __launch_bounds__(128) lightning_scan_vec_kernel(LightningArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DKP = 8 * (R + 4);                    // a q or k row in shared memory: eight runs of R, each padded by 4
+    constexpr int ROW = 2 * DKP + 16;                   // q | k | 16 values
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, s = tid & 7, col = tid >> 3, j = blockIdx.z * 16 + col;
+    const int dk = a.dk, dv = a.dv;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    const bool live = j < dv;
+    float* S_g = a.state + (((size_t)a.slot_of_seq[b] * a.H + h) * dk) * dv + j;
+    float S[R];
+#pragma unroll
+    for (int ii = 0; ii < R; ++ii) {
+        const int i = s * R + ii;
+        S[ii] = (live && i < dk) ? S_g[(size_t)i * dv] : 0.f;
+    }
+    const float decay = a.decay[h];
+    const T* base = (const T*)a.proj;
+    const int kq = h * dk, kk = a.H * dk + h * dk, kvv = 2 * a.H * dk + h * dv + blockIdx.z * 16;
+    const int qk_units = dk >> 3, units = 2 * qk_units + 2, total = CH * units;       // units of eight elements a token, a chunk
+    constexpr int PERU = (CH * (2 * R + 2) + 127) / 128;                              // at most 8 R / 8 = R units of q and of k a token
+    Pack8<T> stage[PERU];
+    // unit n of a chunk: token n / units; then q (qk_units of them), k, and two units of values.  Gives a valid address
+    // (clamped, so the load carries no condition), where the eight floats go in shared memory, and whether they are real.
+    auto source = [&](int u, int first, bool* real, int* to) -> const T* {
+        const int n = tid + 128 * u, nc = min(n, total - 1), tok = nc / units, x = nc % units;
+        bool ok = n < total && first + tok < t1;
+        const T* row = base + (size_t)min(first + tok, t1 - 1) * a.stride;
+        if (x < 2 * qk_units) {
+            const int g = x < qk_units ? x : x - qk_units, i = g * 8;
+            *to = tok * ROW + (x < qk_units ? 0 : DKP) + (i / R) * (R + 4) + (i % R);
+            *real = ok;
+            return row + (x < qk_units ? kq : kk) + i;
+        }
+        const int c = (x - 2 * qk_units) * 8;
+        ok = ok && blockIdx.z * 16 + c < dv;
+        *to = tok * ROW + 2 * DKP + c;
+        *real = ok;
+        return row + kvv + (ok ? c : 0);
+    };
+    auto request = [&](int first) {
+#pragma unroll
+        for (int u = 0; u < PERU; ++u) {
+            bool real; int to;
+            stage[u].load(source(u, first, &real, &to));
+        }
+    };
+    // rows of the padded q and k areas beyond dk are never written by a unit: zero them once (they are read as factors)
+    for (int e = tid; e < CH * ROW; e += 128) sm[e] = 0.f;
+    if (t0 < t1) request(t0);
+    for (int c0 = t0; c0 < t1; c0 += CH) {
+        __syncthreads();                                // the chunk before has been read from shared memory (or the zeros are in place)
+#pragma unroll
+        for (int u = 0; u < PERU; ++u) {
+            bool real; int to;
+            source(u, c0, &real, &to);
+            if (tid + 128 * u < total) {
+                float v[8];
+                stage[u].get(v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = real ? silu_f(v[i]) : 0.f;
+                *reinterpret_cast<float4*>(sm + to) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(sm + to + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+        __syncthreads();
+        if (c0 + CH < t1) request(c0 + CH);
+        const int n = min(CH, t1 - c0);
+        for (int tt = 0; tt < n; ++tt) {
+            const float* qs = sm + tt * ROW + s * (R + 4);
+            const float* ks = qs + DKP;
+            const float vj = sm[tt * ROW + 2 * DKP + col];
+            float acc = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < R; ii += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + ii), q4 = *reinterpret_cast<const float4*>(qs + ii);
+                S[ii] = fmaf(decay, S[ii], k4.x * vj);         acc = fmaf(S[ii], q4.x, acc);
+                S[ii + 1] = fmaf(decay, S[ii + 1], k4.y * vj); acc = fmaf(S[ii + 1], q4.y, acc);
+                S[ii + 2] = fmaf(decay, S[ii + 2], k4.z * vj); acc = fmaf(S[ii + 2], q4.z, acc);
+                S[ii + 3] = fmaf(decay, S[ii + 3], k4.w * vj); acc = fmaf(S[ii + 3], q4.w, acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + h * dv + j] = acc;
         }
     }
@@ -147,8 +276,29 @@ int launch_one(const LightningArgs& a, dim3 grid, cudaStream_t stream) {
 
 // Rows of the state a thread keeps (a quarter of dk, rounded up to 8, 16, 32 or 64) and tokens staged at a time: sixteen for
 // prompts, one for steps of single tokens (nothing to amortise, and less to request).
+template <typename T, int R, int CH>
+int launch_vec(const LightningArgs& a, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)CH * (2 * 8 * (R + 4) + 16) * sizeof(float);
+    static_assert(smem <= 48 * 1024, "the staging area fits the default shared memory");
+    dim3 grid(a.B, a.H, (a.dv + 15) / 16);
+    tb_launch(lightning_scan_vec_kernel<T, R, CH>, grid, 128, smem, stream, a);
+    return 0;
+}
+
 template <typename T>
 int launch_scan(const LightningArgs& a, bool single, cudaStream_t stream) {
+    // sizes in multiples of 8 and rows that 16-byte loads can take: the kernel of eight lanes a column
+    if (a.dk % 8 == 0 && a.dv % 8 == 0 && a.stride % 8 == 0 && ((uintptr_t)a.proj % 16 == 0) && a.dk >= 64 && (a.dv + 15) / 16 <= 65535) {
+        const int rows = a.dk / 8;
+        if (single) {
+            if (rows <= 8) return launch_vec<T, 8, 1>(a, stream);
+            if (rows <= 16) return launch_vec<T, 16, 1>(a, stream);
+            return launch_vec<T, 32, 1>(a, stream);
+        }
+        if (rows <= 8) return launch_vec<T, 8, 16>(a, stream);
+        if (rows <= 16) return launch_vec<T, 16, 16>(a, stream);
+        return launch_vec<T, 32, 8>(a, stream);
+    }
     dim3 grid(a.B, a.H, (a.dv + 31) / 32);
     const int rows = (a.dk + 3) / 4;
     if (single) {

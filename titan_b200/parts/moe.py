@@ -111,11 +111,15 @@ class MixtureOfExperts(FeedForward):
             offsets = plan.offsets.tolist()
             xs = ctx.empty((P, H))
             K.moe_gather(h, plan, top, xs, ctx.stream)
-            for e in range(E):
-                a, b = offsets[e], offsets[e + 1]
-                if b > a:
-                    linear.matmul(xs[a:b], self.w_gate_up[e], act[a:b], linear.EPI_SWIGLU, ctx)
-                    linear.matmul(act[a:b], self.w_down[e], y[a:b], linear.EPI_F32, ctx)
+            if (K.gemm_tc_accepts(xs[:1], self.w_gate_up[0], act[:1], linear.EPI_SWIGLU)
+                    and K.gemm_tc_accepts(act[:1], self.w_down[0], y[:1], linear.EPI_F32)):
+                K.gemm_tc_expert_runs(xs, self.w_gate_up, act, self.w_down, y, offsets, ctx.stream)
+            else:
+                for e in range(E):
+                    a, b = offsets[e], offsets[e + 1]
+                    if b > a:
+                        linear.matmul(xs[a:b], self.w_gate_up[e], act[a:b], linear.EPI_SWIGLU, ctx)
+                        linear.matmul(act[a:b], self.w_down[e], y[a:b], linear.EPI_F32, ctx)
             K.moe_combine(y, wts, shared_y, gate, out, top, ctx.stream, where=plan.inverse)
         else:
             K.moe_grouped(h, self.w_gate_up, act, 0, plan, top, ctx.stream)

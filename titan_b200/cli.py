@@ -30,7 +30,7 @@ def _ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="titan_b200", description="Qwen3-dense generation on one B200: token ids in, token ids out")
+    ap = argparse.ArgumentParser(prog="titan_b200", description="text generation on one B200 for the registered architectures (Qwen3 dense, Tefezen): token ids in, token ids out")
     sub = ap.add_subparsers(dest="command")
     for name in ("run", "chat", "bench"):
         p = sub.add_parser(name, help={"run": "generate from prompt token ids", "chat": "alias of run",

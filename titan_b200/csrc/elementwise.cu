@@ -556,15 +556,50 @@ extern "C" int tb_commit_lengths(const int* slot_of_seq, const int* kv_len, int*
 // Fused with it: ``y`` may be left zeroed (it is the buffer the next sublayer's products add into), and the new
 // residual row may also be written rounded to the compute dtype (``lowp``), which is what the next sublayer's
 // first product reads.  One block per row; the row is read twice (second time from L1/L2).
-template <typename T>
+// VEC: H is a multiple of 4 and a row fits the block's registers (H <= 16 * blockDim): y, x and the weight are requested
+// together as float4 (the weight before the wait for the kernel before: nothing makes it), so a row costs one round trip
+// to memory before the sum and none after it.
+template <typename T, bool VEC>
 __global__ void rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x,
                                    T* __restrict__ lowp, int H, float eps, int zero_y) {
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     float* yr = y + r * H;
     float* xr = x + r * H;
+    if (VEC) {
+        float4 vy[4], vx[4], vw[4];
+        const int n4 = H >> 2;
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            vw[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : zero4;
+        }
+        pdl_wait();
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            vy[j] = i < n4 ? reinterpret_cast<const float4*>(yr)[i] : zero4;
+            vx[j] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : zero4;
+            ss += vy[j].x * vy[j].x + vy[j].y * vy[j].y + vy[j].z * vy[j].z + vy[j].w * vy[j].w;
+        }
+        ss = block_sum(ss, red);
+        const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i >= n4) continue;
+            const float4 v = make_float4(vx[j].x + vy[j].x * scale * vw[j].x, vx[j].y + vy[j].y * scale * vw[j].y,
+                                         vx[j].z + vy[j].z * scale * vw[j].z, vx[j].w + vy[j].w * scale * vw[j].w);
+            reinterpret_cast<float4*>(xr)[i] = v;
+            if (lowp) store4<T>(lowp + r * H + 4 * i, v.x, v.y, v.z, v.w);
+            if (zero_y) reinterpret_cast<float4*>(yr)[i] = zero4;
+        }
+        return;
+    }
+    pdl_wait();
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = yr[i]; ss += v * v; }
     ss = block_sum(ss, red);
@@ -577,12 +612,20 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ y, const float* __restric
     }
 }
 
+template <typename T>
+static void launch_rmsnorm_add(float* y, const float* w, float* x, T* lowp, int n_rows, int H, float eps, int zero_y, cudaStream_t stream) {
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 64 : 32));
+    const bool vec = (H % 4 == 0) && H <= 16 * threads && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                     (!lowp || (uintptr_t)lowp % 16 == 0);
+    if (vec) tb_launch(rmsnorm_add_kernel<T, true>, n_rows, threads, 0, stream, y, w, x, lowp, H, eps, zero_y);
+    else tb_launch(rmsnorm_add_kernel<T, false>, n_rows, threads, 0, stream, y, w, x, lowp, H, eps, zero_y);
+}
+
 extern "C" int tb_rmsnorm_add(float* y, const float* w, float* x, void* lowp, int lowp_dtype, int n_rows, int H,
                               float eps, int zero_y, cudaStream_t stream) {
     TB_REQUIRE(n_rows > 0 && H > 0 && y && w && x, "rmsnorm_add: sizes must be positive (rows=%d H=%d)", n_rows, H);
-    const int threads = H >= 2048 ? 256 : (H >= 512 ? 128 : 64);
-    if (!lowp || lowp_dtype == TB_F32) tb_launch(rmsnorm_add_kernel<float>, n_rows, threads, 0, stream, y, w, x, (float*)lowp, H, eps, zero_y);
-    else if (lowp_dtype == TB_BF16) tb_launch(rmsnorm_add_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, y, w, x, (__nv_bfloat16*)lowp, H, eps, zero_y);
+    if (!lowp || lowp_dtype == TB_F32) launch_rmsnorm_add<float>(y, w, x, (float*)lowp, n_rows, H, eps, zero_y, stream);
+    else if (lowp_dtype == TB_BF16) launch_rmsnorm_add<__nv_bfloat16>(y, w, x, (__nv_bfloat16*)lowp, n_rows, H, eps, zero_y, stream);
     else TB_REQUIRE(false, "rmsnorm_add: unknown dtype %d", lowp_dtype);
     TB_CHECK_LAUNCH("rmsnorm_add");
     return 0;

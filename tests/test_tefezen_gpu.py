@@ -562,3 +562,24 @@ def test_trace_runner_on_a_model_folder(tmp_path, dtype):
             got[en["id"]].append(r)
     for k, t in reqs.items():
         close(torch.stack(got[k]), w.plain(t)[30:], dtype, f"request {k} decoded")
+
+
+def test_command_line_generates_from_a_folder_and_from_random_weights(tmp_path):
+    """bin/titan_b200 run: a model folder of this design (greedy tokens equal the engine's own), and random weights made from
+    its config.json alone."""
+    w = world("small")
+    folder = write_folder(str(tmp_path / "model"), w.cfg, w.weights)
+    prompt = w.requests[1]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "titan_b200"), "run"]
+    common = ["--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "7", "-t", "0", "--repetition-penalty", "1.0", "--dtype", "float32", "-c", "256"]
+    p = subprocess.run(cmd + ["-m", folder] + common, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    made = json.loads(p.stdout.strip().splitlines()[0])["tokens"]
+    assert len(made) == 7
+    logits = w.plain(list(prompt) + made)
+    for k, tok in enumerate(made):
+        row = logits[len(prompt) - 1 + k]
+        assert tok == int(row.argmax()) or float(row.max() - row[tok]) < 1e-3 * float(row.abs().max())
+    p = subprocess.run(cmd + ["--random", os.path.join(folder, "config.json"), "--weights-seed", "3"] + common, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len(json.loads(p.stdout.strip().splitlines()[0])["tokens"]) == 7

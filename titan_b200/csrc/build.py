@@ -1,9 +1,12 @@
-"""Compiles the CUDA sources of this folder for sm_100a into two shared libraries and loads them.
+"""Compiles the CUDA sources of this folder for sm_100a into three shared libraries and loads them.
 
 ``core`` (``_build/libtitan_b200.so``): what every model needs in either dtype (element-wise kernels,
-the CUDA-core matrix product and attention, sampling).  ``tensor``
-(``_build/libtitan_b200_tensor.so``): the tcgen05 / TMA / mma.sync kernels that bfloat16 runs use; it
-is built and loaded when the first of them is asked for, so a float32 run never compiles it.  Each is
+the CUDA-core matrix product and attention, the mixers' and experts' own kernels, sampling).  ``tensor``
+(``_build/libtitan_b200_tensor.so``): the tcgen05 / TMA matrix product that bfloat16 runs use.
+``attention`` (``_build/libtitan_b200_attention.so``): the tensor-core attention kernels (tcgen05 and
+mma.sync), for models whose heads they are built for.  ``tensor`` and ``attention`` are built and loaded
+when the first of their kernels is asked for, so a float32 run compiles neither and a bfloat16 model
+whose attention runs on the any-size kernels compiles no tensor-core attention.  Each is
 built in-tree by calling nvcc directly: one object per source, in parallel, then one link.  A stamp
 of the sources' contents decides whether a build is current, so a fresh checkout compiles at its
 first call and later calls only load.  If the tree cannot be
@@ -30,8 +33,9 @@ from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIBS = {"core": "libtitan_b200.so", "tensor": "libtitan_b200_tensor.so"}
-TENSOR_SOURCES = ("gemm_tc.cu", "attention_mma.cu", "attention_tc.cu", "tma_host.cu")
+LIBS = {"core": "libtitan_b200.so", "tensor": "libtitan_b200_tensor.so", "attention": "libtitan_b200_attention.so"}
+SOURCES_OF = {"tensor": ("gemm_tc.cu", "tma_host.cu"), "attention": ("attention_mma.cu", "attention_tc.cu")}
+LOADS_FIRST = {"core": None, "tensor": "core", "attention": "tensor"}
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fvisibility=default"]
@@ -49,7 +53,9 @@ def sources(which: Optional[str] = None) -> List[str]:
     every = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
     if which is None:
         return every
-    return [f for f in every if (f in TENSOR_SOURCES) == (which == "tensor")]
+    if which in SOURCES_OF:
+        return [f for f in every if f in SOURCES_OF[which]]
+    return [f for f in every if not any(f in named for named in SOURCES_OF.values())]
 
 
 def _headers() -> List[str]:
@@ -116,7 +122,8 @@ def build(force: bool = False, verbose_ptxas: bool = False, which: Optional[str]
     """Build what is missing or stale of one library (or of both, ``which=None``); return the path of the last."""
     if which is None:
         build(force, verbose_ptxas, "core")
-        return build(force, verbose_ptxas, "tensor")
+        build(force, verbose_ptxas, "tensor")
+        return build(force, verbose_ptxas, "attention")
     out = build_dir()
     lib = os.path.join(out, LIBS[which])
     stamp_file = os.path.join(out, f"stamp_{which}.txt")
@@ -159,11 +166,12 @@ def build(force: bool = False, verbose_ptxas: bool = False, which: Optional[str]
 
 def load(which: str = "core") -> ctypes.CDLL:
     """The loaded library; builds it first if need be.  Raises if that fails.  ``tensor`` loads ``core``
-    first (with global symbols: error reporting, launch settings and the merge kernel live there)."""
+    first and ``attention`` loads ``tensor`` first (with global symbols: error reporting, launch settings and the
+    merge kernel live in core, the tensor maps' maker in tensor)."""
     with _lock:
         if which not in _libs:
-            if which == "tensor":
-                load("core")
+            if LOADS_FIRST[which]:
+                load(LOADS_FIRST[which])
             path = build(which=which)
             try:
                 _libs[which] = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)

@@ -44,9 +44,8 @@ def timeline_attach(buffer: Optional[torch.Tensor]) -> bool:
     """Names the buffer (int64, 1 + 8 * records) in which the decode kernels' timeline probe keeps its records, or
     takes it away (None).  False if the tensor-core library was built without the probe (csrc/timeline.cuh: it is
     compiled in with TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE and costs nothing otherwise)."""
-    lib_ = tlib()
     ptr = None if buffer is None else buffer.data_ptr()
-    on = [int(f(c_void_p(ptr))) for f in (lib_.tb_gemm_tc_timeline, lib_.tb_attn_mma_timeline)]
+    on = [int(f(c_void_p(ptr))) for f in (tlib().tb_gemm_tc_timeline, alib().tb_attn_mma_timeline)]
     return all(v == 1 for v in on)
 
 
@@ -177,6 +176,23 @@ def tlib():
         l.tb_gemm_tc_segments.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_tc_expert_runs.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        _tlib = l
+    return _tlib
+
+
+_alib = None
+
+# (own key dims, shared key dims, value dims) of a head that the tensor-core prompt kernel with keys in two parts is built for;
+# asked before the attention library is built, so that a model of other sizes never compiles it
+ATTN_SPLIT_SIZES = {(128, 64, 128)}
+
+
+def alib():
+    """The library of tensor-core attention kernels (tcgen05 and mma.sync), built and loaded when first asked for."""
+    global _alib
+    if _alib is None:
+        tlib()
+        l = _build.load("attention")
         l.tb_attn_decode_mma.argtypes = [POINTER(AttnArgs), c_void_p]
         l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
         l.tb_attn_prefill_mma.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
@@ -185,8 +201,8 @@ def tlib():
         l.tb_attn_prefill_split_check.argtypes = [POINTER(SplitAttnArgs)]
         l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
-        _tlib = l
-    return _tlib
+        _alib = l
+    return _alib
 
 
 def _check(rc: int) -> None:
@@ -525,24 +541,24 @@ def attn_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
 
 
 def attn_decode_mma_accepts(args: AttnArgs, dtype: torch.dtype) -> bool:
-    return dtype == torch.bfloat16 and tlib().tb_attn_decode_mma_check(byref(args), BF16) == 0
+    return dtype == torch.bfloat16 and alib().tb_attn_decode_mma_check(byref(args), BF16) == 0
 
 
 def attn_decode_mma(args: AttnArgs, stream: int) -> None:
     """Decode attention on tensor cores (bfloat16, head_dim 64 or 128), then the merge of the splits."""
-    _check(tlib().tb_attn_decode_mma(byref(args), stream))
+    _check(alib().tb_attn_decode_mma(byref(args), stream))
 
 
 def set_attn_decode_cluster(on: bool) -> None:
     """Decode attention with up to 16 splits: merge them inside a thread-block cluster (on by default) or through
     scratch memory and the merge kernel."""
-    tlib().tb_attn_decode_set_cluster(int(bool(on)))
+    alib().tb_attn_decode_set_cluster(int(bool(on)))
 
 
 def set_attn_decode_late_trigger(on: bool) -> None:
     """Decode attention lets the kernel after it start once its own pages have been requested and read (on by
     default), or at once: the next kernel's first weight requests then queue in front of the pages."""
-    tlib().tb_attn_decode_set_late_trigger(int(bool(on)))
+    alib().tb_attn_decode_set_late_trigger(int(bool(on)))
 
 
 # Where the tensor-core prompt kernels take keys and values from: nowhere they can (0), the step's own rows (every
@@ -551,39 +567,39 @@ KV_NOWHERE, KV_FROM_STEP, KV_FROM_CACHE = 0, 1, 2
 
 
 def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, source: int) -> bool:
-    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_mma_check(byref(args), BF16, int(source)) == 0
+    return dtype == torch.bfloat16 and alib().tb_attn_prefill_mma_check(byref(args), BF16, int(source)) == 0
 
 
 def attn_prefill_mma(args: AttnArgs, source: int, stream: int) -> None:
     """Causal attention of prompts and continuation chunks on tensor cores (bfloat16, head_dim 64 or 128)."""
-    _check(tlib().tb_attn_prefill_mma(byref(args), int(source), stream))
+    _check(alib().tb_attn_prefill_mma(byref(args), int(source), stream))
 
 
 def attn_prefill_split_accepts(args: "SplitAttnArgs") -> bool:
-    return tlib().tb_attn_prefill_split_check(byref(args)) == 0
+    return alib().tb_attn_prefill_split_check(byref(args)) == 0
 
 
 def attn_prefill_split(args: "SplitAttnArgs", stream: int) -> None:
     """Causal (windowed) attention of prompts that start at position 0 on tensor cores, a key being [a part of its own head |
     a part all heads share] and values of their own width (bfloat16; keys of 128 + 64, values of 128)."""
-    _check(tlib().tb_attn_prefill_split(byref(args), stream))
+    _check(alib().tb_attn_prefill_split(byref(args), stream))
 
 
 def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, source: int) -> bool:
-    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_tc_check(byref(args), BF16, int(source)) == 0
+    return dtype == torch.bfloat16 and alib().tb_attn_prefill_tc_check(byref(args), BF16, int(source)) == 0
 
 
 def attn_prefill_tc(args: AttnArgs, source: int, stream: int) -> None:
     """Causal attention of prompts and continuation chunks on the tcgen05 tensor cores (bfloat16, head_dim 128)."""
-    _check(tlib().tb_attn_prefill_tc(byref(args), int(source), stream))
+    _check(alib().tb_attn_prefill_tc(byref(args), int(source), stream))
 
 
 def attn_tc_error() -> int:
-    return int(tlib().tb_attn_tc_error())
+    return int(alib().tb_attn_tc_error())
 
 
 def attn_mma_error() -> int:
-    return int(tlib().tb_attn_mma_error())
+    return int(alib().tb_attn_mma_error())
 
 
 def sample(args: SampleArgs, stream: int) -> None:
@@ -617,7 +633,9 @@ def wait_errors() -> dict:
     if the tensor-core library was never loaded."""
     if _tlib is None:
         return {}
-    found = {"gemm_tc": gemm_tc_error(), "attn_prefill_tc": attn_tc_error(), "attn_mma": attn_mma_error()}
+    found = {"gemm_tc": gemm_tc_error()}
+    if _alib is not None:
+        found.update({"attn_prefill_tc": attn_tc_error(), "attn_mma": attn_mma_error()})
     return {k: v for k, v in found.items() if v}
 
 

@@ -114,7 +114,8 @@ class LatentAttentionMixer(Mixer):
     def _split_args(self, ctx, q_full, kv, rows, o):
         """Arguments of the tensor-core prompt kernel that scores expanded keys (or None where it does not apply)."""
         s, lay = self.spec, ctx.layout
-        if (self.w_ukv is None or not lay.all_fresh or lay.all_single or ctx.options.get("attention", "fast") == "plain"
+        if ((self.dn, self.rd, self.dv) not in K.ATTN_SPLIT_SIZES or self.w_ukv is None or not lay.all_fresh or lay.all_single
+                or ctx.options.get("attention", "fast") == "plain"
                 or ctx.options.get("gemm", "fast") == "plain" or getattr(K, "attn_prefill_split", None) is None):
             return None
         a = K.SplitAttnArgs()

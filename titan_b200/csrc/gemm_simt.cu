@@ -108,10 +108,10 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx
 }
 
 // A few rows (decode steps): a warp per output element of one row and one product of the batch, lanes along K with
-// 16-byte loads where the rows allow; the weights are read once per row of X through L2.  STORE epilogue only.
-template <typename T>
+// 16-byte loads where the rows allow; the weights are read once per row of X through L2.  Epilogues STORE, F32 and ADD.
+template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
-gemm_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict__ out, int M, int N, int K, int ldx, int ldo,
+gemm_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restrict__ out_, int M, int N, int K, int ldx, int ldo,
                  long long sx, long long sw, long long so) {
     pdl_launch_dependents();
     pdl_wait();
@@ -141,7 +141,24 @@ gemm_rows_kernel(const T* __restrict__ X, const T* __restrict__ W, T* __restrict
         for (int k = lane; k < K; k += 32) acc = fmaf(ldf(x + k), ldf(w + k), acc);
     }
     acc = warp_sum(acc);
-    if (lane == 0) stf(out + (size_t)z * so + (size_t)m * ldo + n, acc);
+    if (lane != 0) return;
+    const size_t at = (size_t)z * so + (size_t)m * ldo + n;
+    if (EPI == TB_EPI_STORE) stf((T*)out_ + at, acc);
+    if (EPI == TB_EPI_F32) ((float*)out_)[at] = acc;
+    if (EPI == TB_EPI_ADD) ((float*)out_)[at] += acc;
+}
+
+template <typename T>
+static int launch_rows(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi, int batch,
+                       long long sx, long long sw, long long so, cudaStream_t stream) {
+    dim3 grid((N + 7) / 8, M, batch);
+    const T* x = (const T*)X;
+    const T* w = (const T*)W;
+    if (epi == TB_EPI_STORE) tb_launch(gemm_rows_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so);
+    else if (epi == TB_EPI_F32) tb_launch(gemm_rows_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so);
+    else if (epi == TB_EPI_ADD) tb_launch(gemm_rows_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so);
+    else { tb_set_error("gemm_rows: epilogue %d is not one of store, float32, add", epi); return 1; }
+    return 0;
 }
 
 }  // namespace
@@ -156,10 +173,11 @@ extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int
     TB_REQUIRE(epi != TB_EPI_SWIGLU || N % 2 == 0, "gemm: the SwiGLU epilogue needs an even N, found %d", N);
     TB_REQUIRE((M + BM - 1) / BM <= 65535, "gemm: M=%d is too large for one launch", M);
     if (epi == TB_EPI_STORE && M <= 16 && batch > 1 && (N + 7) / 8 <= 65535) {      // a decode step's rows: a warp per output
-        dim3 grid((N + 7) / 8, M, batch);
-        if (dtype == TB_F32) tb_launch(gemm_rows_kernel<float>, grid, 256, 0, stream, (const float*)X, (const float*)W, (float*)out, M, N, K, ldx, ldo, sx, sw, so);
-        else if (dtype == TB_BF16) tb_launch(gemm_rows_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, M, N, K, ldx, ldo, sx, sw, so);
+        int r;
+        if (dtype == TB_F32) r = launch_rows<float>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
+        else if (dtype == TB_BF16) r = launch_rows<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
         else { tb_set_error("gemm: unknown dtype %d", dtype); return 1; }
+        if (r) return r;
         TB_CHECK_LAUNCH("gemm_rows");
         return 0;
     }
@@ -175,4 +193,19 @@ extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int
 extern "C" int tb_gemm_simt(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
                             int ldo, int epi, cudaStream_t stream) {
     return tb_gemm_simt_batched(X, W, out, dtype, M, N, K, ldx, ldo, epi, 1, 0, 0, 0, stream);
+}
+
+// out (epilogue store, float32 or add) = X[M,K] . W[N,K]^T for a few rows and a small matrix, a warp per output element:
+// the products of a decode step whose matrices are too small to pay for a tensor-core launch (a router, a narrow gate).
+extern "C" int tb_gemm_rows(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx, int ldo, int epi,
+                            cudaStream_t stream) {
+    TB_REQUIRE(M > 0 && N > 0 && K > 0 && M <= 65535 && (N + 7) / 8 <= 2147483647, "gemm_rows: sizes (M=%d N=%d K=%d)", M, N, K);
+    TB_REQUIRE(ldx >= K, "gemm_rows: row stride %d of X is shorter than K=%d", ldx, K);
+    int r;
+    if (dtype == TB_F32) r = launch_rows<float>(X, W, out, M, N, K, ldx, ldo, epi, 1, 0, 0, 0, stream);
+    else if (dtype == TB_BF16) r = launch_rows<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, 1, 0, 0, 0, stream);
+    else { tb_set_error("gemm_rows: unknown dtype %d", dtype); return 1; }
+    if (r) return r;
+    TB_CHECK_LAUNCH("gemm_rows");
+    return 0;
 }

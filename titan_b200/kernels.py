@@ -134,6 +134,7 @@ def lib():
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_longlong, c_longlong, c_longlong, c_void_p]
+        l.tb_gemm_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_rmsnorm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p]
         l.tb_round_rows.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p]
         l.tb_gelu_mul_table.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
@@ -293,6 +294,19 @@ def gemm_simt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: 
     N = w.shape[1]
     _check(lib().tb_gemm_simt_batched(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K, x.stride(0),
                                       out.stride(0), epi, batch, x_step, N * K, out_step, stream))
+
+
+def gemm_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int) -> None:
+    """out (epilogue store, float32 or add) = x[M,K] . w[N,K]^T, a warp per output element: for the few rows of a decode step and
+    matrices too small to pay for a tensor-core launch."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    if w.shape[1] != K or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1 or x.dtype != w.dtype:
+        raise KernelError(f"gemm_rows: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
+    want = w.dtype if epi == EPI_STORE else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm_rows: this epilogue writes {want}, the output is {out.dtype}")
+    _check(lib().tb_gemm_rows(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, w.shape[0], K, x.stride(0), out.stride(0), epi, stream))
 
 
 def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, x: torch.Tensor, eps: float, stream: int,

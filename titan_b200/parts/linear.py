@@ -1,6 +1,7 @@
 """Matrix products of the parts: ``out = epilogue(x . w^T)``.
 
-One function, so that which kernel runs is decided in one place.  float32
+One function, so that which kernel runs is decided in one place.  A few rows times a small matrix (a decode step's router,
+a narrow gate) take the warp-per-output kernel in either dtype.  Otherwise float32
 always takes the CUDA-core kernel (true 32-bit).  bfloat16 takes the tcgen05
 tensor-core kernel when the shapes meet its alignment rules and the CUDA-core
 kernel otherwise; ``ctx.options["gemm"] = "plain"`` forces the latter.
@@ -14,7 +15,16 @@ from .. import kernels as K
 EPI_STORE, EPI_F32, EPI_ADD, EPI_SWIGLU = K.EPI_STORE, K.EPI_F32, K.EPI_ADD, K.EPI_SWIGLU
 
 
+# A product of at most this many rows with a matrix of at most this many elements runs a warp per output element: the fixed
+# cost of a tensor-core launch (or, in float32, of 64 x 64 tiles with a few live rows) is more than such a product's work.
+ROWS_MAX_M, ROWS_MAX_ELEMENTS = 8, 1 << 19
+
+
 def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, ctx) -> None:
+    if (x.shape[0] <= ROWS_MAX_M and w.shape[0] * w.shape[1] <= ROWS_MAX_ELEMENTS and epi in (EPI_STORE, EPI_F32, EPI_ADD)
+            and ctx.options.get("small_products", True)):
+        K.gemm_rows(x, w, out, epi, ctx.stream)
+        return
     if w.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain":
         fast = getattr(K, "gemm_tc", None)
         if fast is not None and K.gemm_tc_accepts(x, w, out, epi):

@@ -679,3 +679,56 @@ extern "C" int tb_gelu_mul_table(const void* z, const void* table, const int* to
     TB_CHECK_LAUNCH("gelu_mul_table");
     return 0;
 }
+
+// The same gate for the few rows of a decode step, with its product: g[t][d] = act(W[d] . x[t]) * table[token[t]][offset + d], a warp
+// per output element, float32 sums of 16-byte loads (the product's result is not rounded before the activation).
+template <typename T>
+__global__ void __launch_bounds__(256) token_gate_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, int K,
+                                                              const T* __restrict__ table, const int* __restrict__ tokens, T* __restrict__ g,
+                                                              int D, int ld_table, int offset, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int d = blockIdx.x * 8 + warp, t = blockIdx.y;
+    if (d >= D) return;
+    const T* x = X + (size_t)t * ldx;
+    const T* w = W + (size_t)d * K;
+    float s = 0.f;
+    constexpr int PER = 16 / sizeof(T);
+    if (K % PER == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) {
+        for (int k = lane * PER; k < K; k += 32 * PER) {
+            if (sizeof(T) == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(x + k), b = *reinterpret_cast<const float4*>(w + k);
+                s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+            } else {
+                const uint4 a = *reinterpret_cast<const uint4*>(x + k), b = *reinterpret_cast<const uint4*>(w + k);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), s);
+                    s = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), s);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) s = fmaf(ldf(w + k), ldf(x + k), s);
+    }
+    s = warp_sum(s);
+    if (lane != 0) return;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+    const float inner = 0.7978845608028654f * (s + 0.044715f * s * s * s);
+    stf(g + (size_t)t * D + d, 0.5f * s * (1.0f + tanhf(inner)) * ldf(table + (size_t)tok * ld_table + offset + d));
+}
+
+extern "C" int tb_token_gate_rows(const void* X, int ldx, const void* W, const void* table, const int* tokens, void* g, int dtype, int T_,
+                                  int K, int D, int ld_table, int offset, int V, cudaStream_t stream) {
+    TB_REQUIRE(T_ > 0 && T_ <= 65535 && D > 0 && K > 0 && V > 0 && offset >= 0 && offset + D <= ld_table && ldx >= K,
+               "token_gate_rows: columns %d..%d of a table %d wide", offset, offset + D, ld_table);
+    dim3 grid((D + 7) / 8, T_);
+    if (dtype == TB_F32) tb_launch(token_gate_rows_kernel<float>, grid, 256, 0, stream, (const float*)X, ldx, (const float*)W, K, (const float*)table, tokens, (float*)g, D, ld_table, offset, V);
+    else if (dtype == TB_BF16) tb_launch(token_gate_rows_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, K, (const __nv_bfloat16*)table, tokens, (__nv_bfloat16*)g, D, ld_table, offset, V);
+    else TB_REQUIRE(false, "token_gate_rows: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("token_gate_rows");
+    return 0;
+}

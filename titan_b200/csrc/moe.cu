@@ -37,18 +37,9 @@ template <> __device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_b
 }
 
 // ------------------------------------------------------------------ route
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int has_gate,
-                                                        int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int T_) {
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ float sm[];           // per warp: E logits
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= T_) return;
-    float* mine = sm + (size_t)warp * E;
-    const float* row = z + (size_t)t * ldz;
-    for (int e = lane; e < E; e += 32) mine[e] = row[e];
-    __syncwarp();
+// One warp, the row's E logits in shared memory (``mine``; destroyed): the ``top`` largest, their softmax, the gate's sigmoid.
+__device__ __forceinline__ void route_row(float* mine, int E, int top, int has_gate, float gate_logit, int* __restrict__ ids,
+                                          float* __restrict__ wts, float* __restrict__ gate, int t, int lane) {
     float first = 0.f, total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -FLT_MAX; int at = 0x7fffffff;
@@ -71,7 +62,22 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     const float inv = 1.0f / total;
     __syncwarp();
     for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= inv;
-    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-row[E]));
+    if (has_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-gate_logit));
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int has_gate,
+                                                        int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gate, int T_) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];           // per warp: E logits
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T_) return;
+    float* mine = sm + (size_t)warp * E;
+    const float* row = z + (size_t)t * ldz;
+    for (int e = lane; e < E; e += 32) mine[e] = row[e];
+    __syncwarp();
+    route_row(mine, E, top, has_gate, has_gate ? row[E] : 0.f, ids, wts, gate, t, lane);
 }
 
 // ------------------------------------------------------------------ plan

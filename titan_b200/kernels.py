@@ -143,6 +143,7 @@ def lib():
         l.tb_lightning_scan.argtypes = [POINTER(LightningArgs), c_int, c_void_p]
         l.tb_gated_rmsnorm.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]
         l.tb_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_token_gate_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_moe_plan_tiles.argtypes = [c_int, c_int]
         l.tb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         l.tb_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
@@ -367,6 +368,15 @@ def moe_route(z: torch.Tensor, experts: int, top: int, has_gate: bool, ids: torc
     _need_cuda(z, ids, wts, gate)
     _check(lib().tb_moe_route(z.data_ptr(), z.stride(0), experts, top, int(has_gate), ids.data_ptr(), wts.data_ptr(), _ptr(gate),
                               z.shape[0], stream))
+
+
+def token_gate_rows(x: torch.Tensor, w: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, offset: int, g: torch.Tensor, stream: int) -> None:
+    """g[t] = gelu_tanh(x[t] . w^T) * table[tokens[t], offset : offset + D] in one kernel, for a few rows (one dtype throughout)."""
+    _need_cuda(x, w, table, tokens, g)
+    if not (w.is_contiguous() and g.is_contiguous() and table.is_contiguous()) or x.stride(1) != 1 or len({x.dtype, w.dtype, table.dtype, g.dtype}) != 1:
+        raise KernelError("token_gate_rows: contiguous tensors of one dtype are wanted")
+    _check(lib().tb_token_gate_rows(x.data_ptr(), x.stride(0), w.data_ptr(), table.data_ptr(), tokens.data_ptr(), g.data_ptr(), dtype_code(w.dtype),
+                                    x.shape[0], x.shape[1], w.shape[0], table.shape[1], int(offset), table.shape[0], stream))
 
 
 def moe_plan_tiles(pairs: int, experts: int) -> int:

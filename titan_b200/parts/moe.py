@@ -83,11 +83,11 @@ class MixtureOfExperts(FeedForward):
         T, H, top, E = h.shape[0], self.spec.hidden_size, self.top, self.E
         P = T * top
         f32, i32 = torch.float32, torch.int32
+        ids, wts = ctx.empty((T, top), i32), ctx.empty((T, top), f32)
+        gate = ctx.empty((T,), f32) if self.shared_F else None
         n_logits = self.w_router.shape[0]
         z = ctx.empty((T, -(-n_logits // 4) * 4), f32)[:, :n_logits]       # rows of whole 16 bytes: the tensor-core product's output rule
         linear.matmul(h, self.w_router, z, linear.EPI_F32, ctx)
-        ids, wts = ctx.empty((T, top), i32), ctx.empty((T, top), f32)
-        gate = ctx.empty((T,), f32) if self.shared_F else None
         K.moe_route(z, E, top, bool(self.shared_F), ids, wts, gate, ctx.stream)
         shared_y = None
         if self.shared_F:

@@ -41,10 +41,13 @@ class TokenTableInput(FeedForward):
 
     def forward(self, h, ctx, out) -> None:
         T = h.shape[0]
-        z = ctx.empty((T, self.D))
-        linear.matmul(h, self.w_gate, z, linear.EPI_STORE, ctx)
         g = ctx.empty((T, self.D))
-        K.gelu_mul_table(z, self.table, ctx.layout.tokens, self.offset, g, ctx.stream)
+        if T <= linear.ROWS_MAX_M and ctx.options.get("small_products", True):      # a decode step: the gate's product and the gate in one kernel
+            K.token_gate_rows(h, self.w_gate, self.table, ctx.layout.tokens, self.offset, g, ctx.stream)
+        else:
+            z = ctx.empty((T, self.D))
+            linear.matmul(h, self.w_gate, z, linear.EPI_STORE, ctx)
+            K.gelu_mul_table(z, self.table, ctx.layout.tokens, self.offset, g, ctx.stream)
         linear.matmul(g, self.w_proj, out, linear.EPI_ADD, ctx)
 
 

@@ -598,7 +598,7 @@ def launcher_times(engine, torch, K, entries):
     """Device time of every launcher call of one eager step, by launcher name (CUDA events around each call; the calls of
     one name added up): {name: (calls, microseconds)}."""
     names = [n for n in ("embed", "scale_f32", "rmsnorm", "rmsnorm_add", "round_rows", "gelu_mul_table", "gemm_simt", "gemm_simt_batched", "gemm_rows",
-                         "gemm_tc", "gemm_tc_segments", "gemm_tc_expert_runs", "gemm_tc_normed", "qk_norm_rope", "kv_append", "attn_prefill", "attn_decode", "attn_decode_mma",
+                         "gemm_tc", "gemm_tc_expert_runs", "gemm_tc_normed", "qk_norm_rope", "kv_append", "attn_prefill", "attn_decode", "attn_decode_mma",
                          "attn_prefill_mma", "attn_prefill_tc", "attn_prefill_split", "moe_gather", "latent_prep", "latent_append", "lightning_scan", "lightning_chunks",
                          "gated_rmsnorm", "moe_route", "token_gate_rows", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc") if hasattr(K, n)]
     events, originals = [], {n: getattr(K, n) for n in names}

@@ -340,6 +340,34 @@ def test_norm_add_kernel_and_batched_product():
             assert float(out[:, hd * 9 + 7: hd * 9 + 9].abs().sum()) == 0.0        # the gap between heads is not written
 
 
+def test_products_and_token_gate_of_a_few_rows():
+    """The warp-per-output kernels of a decode step: a small product with each of its epilogues, and the token gate with
+    its product, at widths that 16-byte loads take and at odd ones."""
+    from titan_b200 import kernels as K
+    g = torch.Generator().manual_seed(14)
+    st = K.current_stream()
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
+        for M, N, Kd in ((1, 33, 64), (5, 7, 50), (8, 130, 136)):
+            x, w = torch.randn(M, Kd, generator=g).to(dt), torch.randn(N, Kd, generator=g).to(dt)
+            ref = x.float() @ w.float().t()
+            out = torch.empty(M, N, dtype=dt, device="cuda")
+            K.gemm_rows(x.cuda(), w.cuda(), out, K.EPI_STORE, st)
+            assert rel_l2(out.float().cpu(), ref) < tol
+            out32 = torch.full((M, N + 3), 2.0, device="cuda")
+            K.gemm_rows(x.cuda(), w.cuda(), out32[:, :N], K.EPI_F32, st)
+            assert rel_l2(out32[:, :N].cpu(), ref) < 1e-5 and float((out32[:, N:] - 2.0).abs().sum()) == 0.0
+            K.gemm_rows(x.cuda(), w.cuda(), out32[:, :N], K.EPI_ADD, st)
+            assert rel_l2(out32[:, :N].cpu(), 2 * ref) < 1e-5
+        for T, D, Kd, off in ((1, 16, 64, 0), (3, 5, 50, 4)):
+            x, w = torch.randn(T, Kd, generator=g).to(dt), (torch.randn(D, Kd, generator=g) / Kd ** 0.5).to(dt)
+            table = torch.randn(11, off + D + 2, generator=g).to(dt)
+            tokens = torch.tensor([10, 0, 3][:T], dtype=torch.int32)
+            ref = P.gelu_tanh(x.double() @ w.double().t()) * table.double()[tokens.long()][:, off:off + D]
+            out = torch.empty(T, D, dtype=dt, device="cuda")
+            K.token_gate_rows(x.cuda(), w.cuda(), table.cuda(), tokens.cuda(), off, out, st)
+            assert rel_l2(out.float().cpu(), ref.float()) < tol
+
+
 # --------------------------------------------------------------------------- #
 # whole models
 # --------------------------------------------------------------------------- #

@@ -1256,25 +1256,6 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
 // Names the buffer of the timeline probe (timeline.cuh); 1 if the library was built with it, 0 if not.
 TB_TIMELINE_SETTER(tb_gemm_tc_timeline)
 
-// Runs of rows of X, each with a matrix of its own: rows [first[s], first[s + 1]) of X times W + s * w_step (elements), into
-// the same rows of out; ``first`` (segments + 1 numbers, on the HOST) ascends.  One tb_gemm_tc per run that has rows,
-// issued from here so that the runs cost a launch each and no interpreter time (the experts of a mixture, whose rows a
-// prompt has gathered side by side).  The output's element size follows from the epilogue.
-extern "C" int tb_gemm_tc_segments(const void* X, int ldx, const void* W, long long w_step, void* out, int ldo, const int* first,
-                                   int segments, int N, int K, int epi, cudaStream_t stream) {
-    TB_REQUIRE(first && segments > 0, "gemm_tc_segments: no segments");
-    const size_t out_bytes = (epi == TB_EPI_STORE || epi == TB_EPI_SWIGLU) ? 2 : 4;
-    for (int s = 0; s < segments; ++s) {
-        const int a = first[s], M = first[s + 1] - a;
-        TB_REQUIRE(M >= 0, "gemm_tc_segments: the segments' first rows must ascend");
-        if (M == 0) continue;
-        const int rc = tb_gemm_tc((const char*)X + (size_t)a * ldx * 2, (const char*)W + (size_t)s * w_step * 2,
-                                  (char*)out + (size_t)a * ldo * out_bytes, M, N, K, ldx, ldo, epi, 0, stream);
-        if (rc) return rc;
-    }
-    return 0;
-}
-
 // The experts of a mixture over rows that a prompt has gathered side by side: for every run s of rows,
 //   act = swiglu(x . Wgu[s]^T)   then   y = act . Wd[s]^T   (float32),
 // two tensor-core products per run, the runs dealt round robin onto a few side streams so that several experts'

@@ -175,7 +175,6 @@ def tlib():
         l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_tc_normed.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         l.tb_gemm_tc_normed_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
-        l.tb_gemm_tc_segments.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_tc_expert_runs.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         _tlib = l
@@ -476,23 +475,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
                             -1 if ordered and not splits else splits, stream))
-
-
-def gemm_tc_segments(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, first, epi: int, stream: int) -> None:
-    """Runs of rows of x, each with a matrix of its own: out[first[s]:first[s + 1]] = epilogue(x[first[s]:first[s + 1]] . w[s]^T),
-    w [segments, N, K] bfloat16, ``first`` a host list of segments + 1 ascending row numbers.  One tensor-core product per
-    run that has rows, issued natively."""
-    global launch_count
-    _need_cuda(x, w, out)
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 3 or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("gemm_tc_segments: bfloat16 rows and a contiguous [segments, N, K] matrix are wanted")
-    want = torch.bfloat16 if epi in (EPI_STORE, EPI_SWIGLU) else torch.float32
-    if out.dtype != want or len(first) != w.shape[0] + 1 or first[-1] > x.shape[0]:
-        raise KernelError("gemm_tc_segments: the output's dtype or the segments do not fit")
-    arr = (c_int * len(first))(*first)
-    launch_count += sum(1 for a, b in zip(first, first[1:]) if b > a) - 1
-    _check(tlib().tb_gemm_tc_segments(x.data_ptr(), x.stride(0), w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), out.stride(0),
-                                     arr, w.shape[0], w.shape[1], w.shape[2], epi, stream))
 
 
 def gemm_tc_expert_runs(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, first, stream: int) -> None:

@@ -33,7 +33,9 @@ def known_architectures():
     return sorted(_ARCHITECTURES)
 
 
-def config_from_dict(d: Dict[str, Any]):
+def config_from_dict(d: Dict[str, Any], shapes=None):
+    """``shapes`` (tensor name -> shape, from a model folder's weight files) goes to a configuration class that says
+    ``reads_tensor_shapes``: a design whose description leaves a size to the shape of a tensor."""
     archs = d.get("architectures")
     if isinstance(d.get("architecture"), str) and not archs:        # some descriptions name it once, as a string
         archs = [d["architecture"]]
@@ -42,7 +44,10 @@ def config_from_dict(d: Dict[str, Any]):
     name = archs[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"architecture '{name}' is not registered; known: {', '.join(known_architectures())}")
-    return _ARCHITECTURES[name].from_dict(d)
+    cls = _ARCHITECTURES[name]
+    if shapes is not None and getattr(cls, "reads_tensor_shapes", False):
+        return cls.from_dict(d, shapes=shapes)
+    return cls.from_dict(d)
 
 
 def load_config(model_dir: str):
@@ -54,4 +59,23 @@ def load_config(model_dir: str):
             d = json.load(f)
         except json.JSONDecodeError as e:
             raise ConfigError(f"{path} is not valid JSON: {e}") from None
-    return config_from_dict(d)
+    return config_from_dict(d, _TensorShapes(model_dir))
+
+
+class _TensorShapes:
+    """name -> shape over a model folder's weight files; the files' headers are read when a shape is first asked for."""
+
+    def __init__(self, model_dir: str):
+        self.model_dir, self._shapes = model_dir, None
+
+    def get(self, name: str, default=None):
+        if self._shapes is None:
+            from ..weights.safetensors_io import open_model_files
+            self._shapes = {}
+            try:
+                for f in open_model_files(self.model_dir):
+                    for n in f.names():
+                        self._shapes[n] = tuple(f.shape(n))
+            except (OSError, ValueError):
+                pass
+        return self._shapes.get(name, default)

@@ -134,6 +134,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a
 #pragma unroll
     for (int j = 0; j < MAXE; ++j) st.acc[j] = 0.f;
     attend_range<T, MAXE>(st, qs, a, lo, pos + 1, first_new, a.batch.q_start[seq], slot, h / (a.nh / a.nkv), lane);
+    if (a.sink) {                                     // one more term of the denominator, against the larger of the two maxima
+        const float sk = a.sink[h], m_new = fmaxf(st.m, sk), alpha = expf(st.m - m_new);
+        st.l = st.l * alpha + expf(sk - m_new);
+#pragma unroll
+        for (int j = 0; j < MAXE; ++j) st.acc[j] *= alpha;
+    }
     const float inv = 1.0f / st.l;
     const int hdv = value_width(a);
     T* o = (T*)a.out + (size_t)t * a.out_stride + h * hdv;
@@ -202,6 +208,8 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     float m = -FLT_MAX;
     for (int s = first; s < used; ++s)
         if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
+    const bool sunk = a.sink != nullptr;
+    if (sunk) m = fmaxf(m, a.sink[h]);
     constexpr int PER = (32 * MAXE + 127) / 128;
     float l = 0.f, acc[PER];
 #pragma unroll
@@ -218,6 +226,7 @@ __global__ void attn_merge_kernel(AttnArgs a) {
             if (d < hd) acc[j] = fmaf(w, p[d], acc[j]);
         }
     }
+    if (sunk) l += expf(a.sink[h] - m);               // the sink counts once, here, not once a split
     const float inv = 1.0f / l;
     T* o = (T*)a.out + (size_t)b * a.out_stride + h * hd;
 #pragma unroll

@@ -40,6 +40,9 @@ struct AttnArgs {
     // over one shared latent) asks for more blocks: block y then takes heads [y * nh / head_blocks, (y + 1) * nh / head_blocks)
     // and reads kv head y * nkv / head_blocks.  Must divide nh and be a multiple of nkv.
     int head_blocks;
+    // A sink in the softmax: sink[h] (float32, one per query head; null: none) joins the denominator of head h as one more
+    // term exp(sink[h] - max), unscaled, without a key and without a value, once per query however the keys are split.
+    const float* sink;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

@@ -734,6 +734,7 @@ extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 :
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
     TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
+    TB_REQUIRE(!a->sink, "attn_decode_mma: a softmax with a sink is not taken here");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
     TB_REQUIRE(a->cache.page_size == PAGE, "attn_decode_mma: pages of %d rows, not %d", PAGE, a->cache.page_size);
@@ -824,6 +825,7 @@ static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, con
 // and values from the pages of a cache that keeps every key, the step's own appended already).
 extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int source) {
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
+    TB_REQUIRE(!a->sink, "attn_prefill_mma: a softmax with a sink is not taken here");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");

@@ -161,7 +161,8 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
     const int head = blockIdx.y * nwarp + warp;
-    const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    const bool touch_v = a.append || a.v_first || a.v_keep;
+    const int n_heads = a.nh + a.nkv + (touch_v ? a.nkv : 0);
     // cosine and sine of this token's angles, once per block: [rot/2] each, behind the warps' rows
     float* cs = head_smem + nwarp * a.hd;
     float* sn = cs + (a.rope.rot >> 1);
@@ -195,26 +196,34 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int seq = a.seq_of[t];
     const int slot = a.slot_of_seq[seq];
     const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
-    if (!is_q && !is_k) {   // V: straight copy into the cache
-        if (!to_cache) return;
-        TOut* dst = (TOut*)a.cache.storage + kv_half_elems(a.cache) + kv_row_offset(a.cache, slot, pos, head - a.nh - a.nkv);
+    if (!is_q && !is_k) {   // V: into the cache as it is, or blended with an earlier layer's values of the same token first
+        const int vh = head - a.nh - a.nkv;
+        TOut* dst = to_cache ? (TOut*)a.cache.storage + kv_half_elems(a.cache) + kv_row_offset(a.cache, slot, pos, vh) : nullptr;
+        const TOut* vf = a.v_first ? (const TOut*)a.v_first + (size_t)t * a.v_first_stride + vh * hd : nullptr;
+        TOut* keep = a.v_keep ? (TOut*)a.v_keep + (size_t)t * a.v_keep_stride + vh * hd : nullptr;
+        const float lam = vf ? *a.v_mix : 0.f;
 #pragma unroll
         for (int j = 0; j < QK_MAXE; ++j) {
             const int e = lane + 32 * j;
-            if (e < hd) stf(dst + e, v[j]);
+            if (e >= hd) continue;
+            const float val = vf ? (1.0f - lam) * v[j] + lam * ldf(vf + e) : v[j];
+            if (keep) stf(keep + e, val);
+            if (dst) stf(dst + e, val);
         }
         return;
     }
     const float* w = is_q ? a.q_w : a.k_w;
+    const bool normed = w || a.norm_dims > 0;
+    const float n_mean = (float)(a.norm_dims > 0 ? a.norm_dims : hd);
     float scale = 1.f;
-    if (w) {
+    if (normed && !a.norm_after) {
         ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)hd + a.eps);
+        scale = 1.0f / sqrtf(ss / n_mean + a.eps);
     }
 #pragma unroll
     for (int j = 0; j < QK_MAXE; ++j) {
         const int e = lane + 32 * j;
-        if (e < hd) y[e] = w ? v[j] * scale * w[e] : v[j];
+        if (e < hd) y[e] = (normed && !a.norm_after) ? v[j] * scale * (w ? w[e] : 1.f) : v[j];
     }
     __syncwarp();
     const int half = a.rope.rot >> 1;
@@ -222,17 +231,30 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
                      : (a.k_out ? (TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * hd : nullptr);
     TOut* cdst = (is_k && to_cache)
                      ? (TOut*)a.cache.storage + kv_row_offset(a.cache, slot, pos, head - a.nh) : nullptr;
+    float turned[QK_MAXE];
+    float ss_after = 0.f;
 #pragma unroll
     for (int j = 0; j < QK_MAXE; ++j) {
         const int e = lane + 32 * j;
-        if (e >= hd) continue;
-        float r = y[e];
-        if (a.rope.inv_freq && e < a.rope.rot) {
+        float r = e < hd ? y[e] : 0.f;
+        if (e < hd && a.rope.inv_freq && e < a.rope.rot) {
             const bool first = e < half;
             const int k = first ? e : e - half;
             const float s = sn[k], c = cs[k];
             r = first ? y[e] * c - y[e + half] * s : y[e - half] * s + y[e] * c;
         }
+        turned[j] = r;
+        ss_after += r * r;
+    }
+    if (normed && a.norm_after) {                     // the unit norm of the rotated head
+        ss_after = warp_sum(ss_after);
+        scale = 1.0f / sqrtf(ss_after / n_mean + a.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < QK_MAXE; ++j) {
+        const int e = lane + 32 * j;
+        if (e >= hd) continue;
+        const float r = (normed && a.norm_after) ? turned[j] * scale * (w ? w[e] : 1.f) : turned[j];
         if (out) stf(out + e, r);
         if (cdst) stf(cdst + e, r);
     }
@@ -438,8 +460,13 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(!a.row_sumsq || (a.row_width > 0 && a.row_parts > 0 && a.T <= 32), "qk_norm_rope: row sums of squares need the rows' width, their number of parts and at most 32 rows");
     TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
                "qk_norm_rope: the cache view does not match the heads");
+    TB_REQUIRE(a.norm_dims >= 0 && a.norm_dims <= a.hd, "qk_norm_rope: a mean over %d of a head's %d elements", a.norm_dims, a.hd);
+    TB_REQUIRE(!a.v_first || a.v_mix, "qk_norm_rope: values to blend with need the blending factor");
+    TB_REQUIRE(!(a.v_first || a.v_keep) || a.nkv > 0, "qk_norm_rope: values are blended or kept only where the rows have V heads");
+    TB_REQUIRE(!(a.zero_in && a.v_keep && in_dtype == out_dtype), "qk_norm_rope: V rows kept in place cannot be zeroed as well");
     const int warps = 4;
-    const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    const bool plain_heads = a.norm_dims == 0 && !a.norm_after && !a.v_first && !a.v_keep;     // what the vector kernel knows
+    const int n_heads = a.nh + a.nkv + ((a.append || a.v_first || a.v_keep) ? a.nkv : 0);
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
     const size_t smem = ((size_t)warps * a.hd + a.rope.rot) * sizeof(float);
     const int in_bytes = in_dtype == TB_F32 ? 4 : 2, out_bytes = out_dtype == TB_F32 ? 4 : 2;
@@ -448,7 +475,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
         const int unit = hv * esz < 16 ? hv * esz : 16;   // read and written in pieces of at most 16 bytes
         return p == nullptr || (((uintptr_t)p % (size_t)unit) == 0 && (stride_elems * esz) % unit == 0);
     };
-    const bool vec = (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rope.rot == a.hd || !a.rope.inv_freq) &&
+    const bool vec = plain_heads && (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rope.rot == a.hd || !a.rope.inv_freq) &&
                      aligned(a.in, a.in_stride, in_bytes) && aligned(a.q_out, a.q_stride, out_bytes) &&
                      aligned(a.k_out, a.k_stride, out_bytes) && aligned(a.cache.storage, a.hd, out_bytes);
     if (in_dtype == TB_F32 && out_dtype == TB_F32) {
@@ -730,5 +757,59 @@ extern "C" int tb_token_gate_rows(const void* X, int ldx, const void* W, const v
     else if (dtype == TB_BF16) tb_launch(token_gate_rows_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)X, ldx, (const __nv_bfloat16*)W, K, (const __nv_bfloat16*)table, tokens, (__nv_bfloat16*)g, D, ld_table, offset, V);
     else TB_REQUIRE(false, "token_gate_rows: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("token_gate_rows");
+    return 0;
+}
+
+// ------------------------------------------------------------------ a norm without statistics, and the scaled residual sum
+// "Dynamic tanh": y = tanh(alpha * x) * w + b, alpha one number (read from the device), no mean and no variance.
+//   tb_dyt        y[r] = D(x[rows ? rows[r] : r])                               (a block a row; float32 in, compute dtype out)
+//   tb_scale_add  x += y * s (s a vector: a sublayer's output scaled element by element before it joins the residual
+//                 stream), y left zeroed for the next sublayer's products to add into if asked, and, given a norm
+//                 (w, b, alpha), the new rows' D(x) written to ``h``: the next sublayer's input in the same pass.
+template <typename T>
+__global__ void __launch_bounds__(256) dyt_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                                  const float* __restrict__ alpha, T* __restrict__ y, const int* __restrict__ rows, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t r = blockIdx.x, src = rows ? (size_t)rows[r] : r;
+    const float al = *alpha;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) stf(y + r * H + i, tanhf(al * x[src * H + i]) * w[i] + b[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) scale_add_kernel(float* __restrict__ y, const float* __restrict__ s, float* __restrict__ x, int zero_y,
+                                                        const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha,
+                                                        T* __restrict__ h, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    const float al = h ? *alpha : 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const size_t at = r * H + i;
+        const float v = fmaf(y[at], s ? s[i] : 1.f, x[at]);
+        x[at] = v;
+        if (zero_y) y[at] = 0.f;
+        if (h) stf(h + at, tanhf(al * v) * w[i] + b[i]);
+    }
+}
+
+extern "C" int tb_dyt(const float* x, const float* w, const float* b, const float* alpha, void* y, int dtype, const int* rows, int n_rows,
+                      int H, cudaStream_t stream) {
+    TB_REQUIRE(n_rows > 0 && H > 0 && x && w && b && alpha && y, "dyt: sizes must be positive and every tensor given");
+    if (dtype == TB_F32) tb_launch(dyt_kernel<float>, n_rows, 256, 0, stream, x, w, b, alpha, (float*)y, rows, H);
+    else if (dtype == TB_BF16) tb_launch(dyt_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, x, w, b, alpha, (__nv_bfloat16*)y, rows, H);
+    else TB_REQUIRE(false, "dyt: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("dyt");
+    return 0;
+}
+
+extern "C" int tb_scale_add(float* y, const float* s, float* x, int zero_y, const float* w, const float* b, const float* alpha, void* h,
+                            int dtype, int n_rows, int H, cudaStream_t stream) {
+    TB_REQUIRE(n_rows > 0 && H > 0 && x && y, "scale_add: sizes must be positive");
+    TB_REQUIRE(!h || (w && b && alpha), "scale_add: the norm of the new rows needs its weight, bias and factor");
+    if (dtype == TB_F32) tb_launch(scale_add_kernel<float>, n_rows, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (float*)h, H);
+    else if (dtype == TB_BF16) tb_launch(scale_add_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (__nv_bfloat16*)h, H);
+    else TB_REQUIRE(false, "scale_add: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("scale_add");
     return 0;
 }

@@ -1,5 +1,6 @@
 // Epilogues shared by the matrix-product kernels (see gemm_simt.cu for their meaning).
 #pragma once
+#include "activation.h"
 #define TB_EPI_STORE 0
 #define TB_EPI_F32 1
 #define TB_EPI_ADD 2

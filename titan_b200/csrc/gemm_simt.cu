@@ -10,7 +10,8 @@
 //   TB_EPI_STORE   out[m][n] = acc                      (compute dtype)
 //   TB_EPI_F32     out[m][n] = acc                      (float32: logits)
 //   TB_EPI_ADD     out[m][n] += acc                     (float32 residual stream, in place)
-//   TB_EPI_SWIGLU  out[m][j] = silu(acc[2j]) * acc[2j+1] (rows of W interleaved gate, up; N even)
+//   TB_EPI_SWIGLU  out[m][j] = gate(acc[2j], acc[2j+1]) (rows of W interleaved gate, up; N even); the gate is
+//                  silu(g) * u unless the launch names another (activation.h)
 #include "common.cuh"
 #include "gemm.h"
 
@@ -21,7 +22,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restrict__ out_,
-                 int M, int N, int K, int ldx, int ldo, long long sx, long long sw, long long so) {
+                 int M, int N, int K, int ldx, int ldo, long long sx, long long sw, long long so, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     // blockIdx.z: one of a batch of products of equal shape (the heads of a mixer, say), each at its own offset
@@ -75,7 +76,7 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restr
                 const int n = n0 + tx * TN + j;
                 if (n + 1 < N) {
                     const float g = acc[i][j], u = acc[i][j + 1];
-                    stf((T*)out + (size_t)m * ldo + n / 2, g / (1.0f + expf(-g)) * u);
+                    stf((T*)out + (size_t)m * ldo + n / 2, tb_gated(act, limit, g, u));
                 }
             }
         } else {
@@ -93,15 +94,15 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restr
 
 template <typename T>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
-           int batch, long long sx, long long sw, long long so, cudaStream_t stream) {
+           int batch, long long sx, long long sw, long long so, int act, float limit, cudaStream_t stream) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     switch (epi) {
-        case TB_EPI_STORE: tb_launch(gemm_simt_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
-        case TB_EPI_F32: tb_launch(gemm_simt_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
-        case TB_EPI_ADD: tb_launch(gemm_simt_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
-        case TB_EPI_SWIGLU: tb_launch(gemm_simt_kernel<T, TB_EPI_SWIGLU>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so); break;
+        case TB_EPI_STORE: tb_launch(gemm_simt_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so, act, limit); break;
+        case TB_EPI_F32: tb_launch(gemm_simt_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so, act, limit); break;
+        case TB_EPI_ADD: tb_launch(gemm_simt_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so, act, limit); break;
+        case TB_EPI_SWIGLU: tb_launch(gemm_simt_kernel<T, TB_EPI_SWIGLU>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo, sx, sw, so, act, limit); break;
         default: tb_set_error("gemm: unknown epilogue %d", epi); return 1;
     }
     return 0;
@@ -165,8 +166,11 @@ static int launch_rows(const void* X, const void* W, void* out, int M, int N, in
 
 // ldx: row stride of X in elements; ldo: row stride of out in elements.  ``batch`` products of the same shape in one
 // launch: product z reads X + z * sx and W + z * sw and writes out + z * so (offsets in elements).
-extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
-                                    int ldo, int epi, int batch, long long sx, long long sw, long long so, cudaStream_t stream) {
+// act, limit: the gate of the SWIGLU epilogue (activation.h).
+extern "C" int tb_gemm_simt_gated(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
+                                  int ldo, int epi, int batch, long long sx, long long sw, long long so, int act, float limit,
+                                  cudaStream_t stream) {
+    TB_REQUIRE(act >= 0 && act < TB_ACT_KINDS, "gemm: unknown gate %d", act);
     TB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: sizes must be positive (M=%d N=%d K=%d)", M, N, K);
     TB_REQUIRE(batch > 0 && batch <= 65535, "gemm: a batch of %d products", batch);
     TB_REQUIRE(ldx >= K, "gemm: row stride %d of X is shorter than K=%d", ldx, K);
@@ -182,12 +186,17 @@ extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int
         return 0;
     }
     int rc;
-    if (dtype == TB_F32) rc = launch<float>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
-    else if (dtype == TB_BF16) rc = launch<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, stream);
+    if (dtype == TB_F32) rc = launch<float>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, act, limit, stream);
+    else if (dtype == TB_BF16) rc = launch<__nv_bfloat16>(X, W, out, M, N, K, ldx, ldo, epi, batch, sx, sw, so, act, limit, stream);
     else { tb_set_error("gemm: unknown dtype %d", dtype); return 1; }
     if (rc) return rc;
     TB_CHECK_LAUNCH("gemm_simt");
     return 0;
+}
+
+extern "C" int tb_gemm_simt_batched(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,
+                                    int ldo, int epi, int batch, long long sx, long long sw, long long so, cudaStream_t stream) {
+    return tb_gemm_simt_gated(X, W, out, dtype, M, N, K, ldx, ldo, epi, batch, sx, sw, so, TB_ACT_SILU, 0.f, stream);
 }
 
 extern "C" int tb_gemm_simt(const void* X, const void* W, void* out, int dtype, int M, int N, int K, int ldx,

@@ -78,7 +78,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
 
 // silu(g) * u with the fast exponential and division: the result is rounded to bfloat16 anyway, and the
 // epilogue warps run one per scheduler, so every instruction here is on the critical path of a tile.
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// Other gates than silu (activation.h) take the same place: the kind and its constant come with the launch.
+#define silu_mul(g, u) tb_gated_fast(a.act, a.limit, (g), (u))
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
@@ -100,6 +101,7 @@ struct TcArgs {
     // 1/sqrt(mean(x^2) + eps) in its epilogue, or (K cut into slices: no CTA sees a whole row) leaves its rows'
     // partial sums of squares at sumsq_out [slice][32] for the consumer of the sums to add up, in slice order, and apply
     const float* xf; int ldxf; const float* norm_w; float* sumsq_out; float norm_eps;
+    int act; float limit;   // the gate of the SWIGLU epilogue (activation.h); 0: silu
 };
 
 // TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
@@ -1120,7 +1122,7 @@ extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w,
     a.out = out; a.rows_a = N; a.rows_b = M; a.K = K; a.ldo = ldo; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
     a.k_blocks_per_split = (kb + s - 1) / s;
     a.atomic = s > 1;
-    a.xf = xf; a.ldxf = ldxf; a.norm_w = norm_w; a.sumsq_out = sumsq_out; a.norm_eps = eps;
+    a.xf = xf; a.ldxf = ldxf; a.norm_w = norm_w; a.sumsq_out = sumsq_out; a.norm_eps = eps; a.act = 0; a.limit = 0.f;
     CUtensorMap ma;
     if (tb_make_map_bf16(&ma, W, N, K, K, BM)) return 1;
     dim3 grid(1, tiles, s);
@@ -1139,9 +1141,11 @@ extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w,
 // splits: K slices (swap mode, ADD epilogue only); 0 = choose; -1 = choose, and add the parts of a sum in a fixed order
 // (swap mode: the slices of a tile form a thread-block cluster; prompt products: no tile is cut along K), so that
 // the same inputs give the same bits on every run.
-extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
-                          int splits, cudaStream_t stream) {
+// act, limit: the gate of the SWIGLU epilogue (activation.h).
+extern "C" int tb_gemm_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
+                                int splits, int act, float limit, cudaStream_t stream) {
     if (tb_gemm_tc_check(M, N, K, ldx, ldo, epi, X, W, out)) return 1;
+    TB_REQUIRE(act >= 0 && act < TB_ACT_KINDS, "gemm_tc: unknown gate %d", act);
     const bool ordered = splits < 0;
     if (ordered) splits = 0;
     const bool swap = M < g_swap_below;
@@ -1149,7 +1153,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     CUtensorMap ma, mb;
     TcArgs a;
     a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
-    a.xf = nullptr; a.ldxf = 0; a.norm_w = nullptr; a.sumsq_out = nullptr; a.norm_eps = 0.f;
+    a.xf = nullptr; a.ldxf = 0; a.norm_w = nullptr; a.sumsq_out = nullptr; a.norm_eps = 0.f; a.act = act; a.limit = limit;
     int rc = 0;
     static int sm_count = 0;
     if (!sm_count) {
@@ -1253,16 +1257,21 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     return 0;
 }
 
+extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
+                          int splits, cudaStream_t stream) {
+    return tb_gemm_tc_gated(X, W, out, M, N, K, ldx, ldo, epi, splits, TB_ACT_SILU, 0.f, stream);
+}
+
 // Names the buffer of the timeline probe (timeline.cuh); 1 if the library was built with it, 0 if not.
 TB_TIMELINE_SETTER(tb_gemm_tc_timeline)
 
 // The experts of a mixture over rows that a prompt has gathered side by side: for every run s of rows,
-//   act = swiglu(x . Wgu[s]^T)   then   y = act . Wd[s]^T   (float32),
+//   act = gate(x . Wgu[s]^T) (activation.h)   then   y = act . Wd[s]^T   (float32),
 // two tensor-core products per run, the runs dealt round robin onto a few side streams so that several experts'
 // products, each too small to fill the machine, run beside one another.  The side streams start after what the
 // caller's stream has queued and the caller's stream goes on after all of them (events; no host wait).
 extern "C" int tb_gemm_tc_expert_runs(const void* X, int ldx, const void* Wgu, void* act, int ld_act, const void* Wd, void* y, int ldy,
-                                      const int* first, int runs, int H, int F, cudaStream_t stream) {
+                                      const int* first, int runs, int H, int F, int gate, float limit, cudaStream_t stream) {
     TB_REQUIRE(first && runs > 0 && H > 0 && F > 0, "gemm_tc_expert_runs: sizes must be positive");
     constexpr int SIDE = 4;
     static cudaStream_t side[SIDE];
@@ -1284,8 +1293,8 @@ extern "C" int tb_gemm_tc_expert_runs(const void* X, int ldx, const void* Wgu, v
         if (M < 0) { tb_set_error("gemm_tc_expert_runs: the runs' first rows must ascend"); rc = 1; break; }
         if (M == 0) continue;
         cudaStream_t st = side[used++ % SIDE];
-        rc = tb_gemm_tc((const char*)X + (size_t)a * ldx * 2, (const char*)Wgu + (size_t)s * 2 * F * H * 2, (char*)act + (size_t)a * ld_act * 2,
-                        M, 2 * F, H, ldx, ld_act, TB_EPI_SWIGLU, 0, st);
+        rc = tb_gemm_tc_gated((const char*)X + (size_t)a * ldx * 2, (const char*)Wgu + (size_t)s * 2 * F * H * 2, (char*)act + (size_t)a * ld_act * 2,
+                              M, 2 * F, H, ldx, ld_act, TB_EPI_SWIGLU, 0, gate, limit, st);
         if (!rc) rc = tb_gemm_tc((const char*)act + (size_t)a * ld_act * 2, (const char*)Wd + (size_t)s * H * F * 2, (char*)y + (size_t)a * ldy * 4,
                                  M, H, F, ld_act, ldy, TB_EPI_F32, 0, st);
     }

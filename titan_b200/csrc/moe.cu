@@ -80,6 +80,82 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     route_row(mine, E, top, has_gate, has_gate ? row[E] : 0.f, ids, wts, gate, t, lane);
 }
 
+// Routing by scores over ALL experts: s = softmax(z) over the row's n_all logits; an expert is chosen by s + correction,
+// and only inside the ``keep`` groups (of n_all / groups neighbours each) whose best such score is largest; the weights
+// are the chosen experts' s over their sum (+ 1e-20).  One warp a token; the lowest index wins a tie.  ``score`` and
+// ``choice`` are the warp's rows in shared memory.
+__global__ void __launch_bounds__(128) moe_route_all_kernel(const float* __restrict__ z, int ldz, int n_all, int top,
+                                                            const float* __restrict__ correction, int groups, int keep,
+                                                            int* __restrict__ ids, float* __restrict__ wts, int T_) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];           // per warp: n_all scores, n_all choice scores, ``groups`` group scores and as many marks
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T_) return;
+    float* score = sm + (size_t)warp * (2 * n_all + 2 * groups);
+    float* choice = score + n_all;
+    float* best_of = choice + n_all;
+    float* kept = best_of + groups;
+    const float* row = z + (size_t)t * ldz;
+    float m = -FLT_MAX;
+    for (int e = lane; e < n_all; e += 32) m = fmaxf(m, row[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < n_all; e += 32) { const float p = expf(row[e] - m); score[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < n_all; e += 32) { score[e] *= inv; choice[e] = score[e] + (correction ? correction[e] : 0.f); }
+    __syncwarp();
+    auto arg_max = [&](const float* v, int n, float* best_out) -> int {
+        float best = -INFINITY; int at = 0x7fffffff;
+        for (int e = lane; e < n; e += 32)
+            if (v[e] > best) { best = v[e]; at = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        *best_out = best;
+        return at;
+    };
+    if (groups > 1 && keep < groups) {
+        const int per = n_all / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
+            best_of[g] = b;
+        }
+        __syncwarp();
+        for (int g = lane; g < groups; g += 32) kept[g] = 0.f;
+        __syncwarp();
+        for (int k = 0; k < keep; ++k) {
+            float b;
+            const int g = arg_max(best_of, groups, &b);
+            __syncwarp();
+            if (lane == 0 && g < groups) { best_of[g] = -INFINITY; kept[g] = 1.f; }
+            __syncwarp();
+        }
+        for (int e = lane; e < n_all; e += 32)
+            if (kept[e / per] == 0.f) choice[e] = -INFINITY;      // minus infinity, not zero: choice scores may be negative
+        __syncwarp();
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float b;
+        const int at = arg_max(choice, n_all, &b);
+        const int e = at < n_all ? at : 0;
+        const float w = score[e];
+        total += w;
+        __syncwarp();
+        if (lane == 0) { ids[(size_t)t * top + k] = e; wts[(size_t)t * top + k] = w; choice[e] = -INFINITY; }
+        __syncwarp();
+    }
+    const float norm = 1.0f / (total + 1e-20f);
+    for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= norm;
+}
+
 // ------------------------------------------------------------------ plan
 // counts [E], rank [P] are scratch; perm [P]; tiles: tile_e, tile_row0, tile_rows [max_tiles]; n_tiles [1].
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ rank,
@@ -140,10 +216,11 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void* __restrict__ out, int ldo,
                    const int* __restrict__ perm, const int* __restrict__ tile_e, const int* __restrict__ tile_row0,
-                   const int* __restrict__ tile_rows, const int* __restrict__ n_tiles, int N, int K, int top) {
+                   const int* __restrict__ tile_rows, const int* __restrict__ n_tiles, int N, int K, int top, int n_real, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     if ((int)blockIdx.y >= *n_tiles) return;
+    if (tile_e[blockIdx.y] >= n_real) return;         // an expert without matrices (its output is its input): nothing to multiply
     __shared__ float xs[MOE_BK][MOE_BM + 4];
     __shared__ float ws[MOE_BK][MOE_BN + 4];
     __shared__ int src[MOE_BM];
@@ -199,7 +276,7 @@ moe_grouped_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, vo
                 const int n = n0 + tx * 4 + j;
                 if (n + 1 < N) {
                     const float g = acc[i][j], u = acc[i][j + 1];
-                    stf(o + n / 2, g / (1.0f + expf(-g)) * u);
+                    stf(o + n / 2, tb_gated(act, limit, g, u));
                 }
             }
         } else {
@@ -218,7 +295,7 @@ moe_grouped_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, vo
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void* __restrict__ out, int ldo,
-                const int* __restrict__ ids, int N_out, int K, int top) {
+                const int* __restrict__ ids, int N_out, int K, int top, int n_real, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -226,6 +303,7 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
     const int n = blockIdx.y * 8 + warp;
     if (n >= N_out) return;
     const int e = ids[p];
+    if (e >= n_real) return;                          // an expert without matrices: the combine kernel adds the input itself
     const T* x = X + (size_t)(MODE == 0 ? p / top : p) * ldx;
     constexpr int PER = 16 / sizeof(T);                 // elements of a 16-byte load
     const bool wide = K % PER == 0 && ldx % PER == 0 && ((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0);
@@ -247,7 +325,7 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
             u = fmaf(ldf(wu + k), xv, u);
         }
         g = warp_sum(g); u = warp_sum(u);
-        if (lane == 0) stf((T*)out + (size_t)p * ldo + n, g / (1.0f + expf(-g)) * u);
+        if (lane == 0) stf((T*)out + (size_t)p * ldo + n, tb_gated(act, limit, g, u));
     } else {
         const T* w = W + ((size_t)e * N_out + n) * K;
         float s = 0.f;
@@ -266,14 +344,19 @@ moe_rows_kernel(const T* __restrict__ X, int ldx, const T* __restrict__ W, void*
 }
 
 // ------------------------------------------------------------------ combine
+// ``ids`` with ``n_real`` and ``x``: a pair whose expert is n_real or beyond has no matrices and no row in y; its output
+// is the token's own input row x[t].
+template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, const float* __restrict__ shared_y,
-                                   const float* __restrict__ gate, float* __restrict__ out, int H, int top, const int* __restrict__ where) {
+                                   const float* __restrict__ gate, float* __restrict__ out, int H, int top, const int* __restrict__ where,
+                                   const int* __restrict__ ids, int n_real, const T* __restrict__ x, int ldx) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
+            if (ids && ids[t * top + k] >= n_real) { s = fmaf(wts[t * top + k], ldf(x + t * ldx + i), s); continue; }
             const size_t row = where ? (size_t)where[t * top + k] : t * top + k;       // pair order, or where the plan put the pair
             s = fmaf(wts[t * top + k], y[row * H + i], s);
         }
@@ -294,6 +377,18 @@ extern "C" int tb_moe_route(const float* z, int ldz, int E, int top, int has_gat
     return 0;
 }
 
+extern "C" int tb_moe_route_all(const float* z, int ldz, int n_all, int top, const float* correction, int groups, int keep,
+                                int* ids, float* wts, int T_, cudaStream_t stream) {
+    TB_REQUIRE(T_ > 0 && n_all > 0 && top > 0 && top <= n_all && n_all <= 2048, "moe_route_all: %d of %d experts (at most 2048)", top, n_all);
+    TB_REQUIRE(groups > 0 && keep > 0 && keep <= groups && n_all % groups == 0, "moe_route_all: %d groups of which %d are kept, over %d experts", groups, keep, n_all);
+    TB_REQUIRE(top <= keep * (n_all / groups), "moe_route_all: %d experts a token out of %d groups of %d", top, keep, n_all / groups);
+    TB_REQUIRE(ldz >= n_all && z && ids && wts, "moe_route_all: missing buffers");
+    tb_launch(moe_route_all_kernel, (T_ + 3) / 4, 128, (size_t)4 * (2 * n_all + 2 * groups) * sizeof(float), stream, z, ldz, n_all, top, correction,
+              groups, keep, ids, wts, T_);
+    TB_CHECK_LAUNCH("moe_route_all");
+    return 0;
+}
+
 extern "C" int tb_moe_plan_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
 
 extern "C" int tb_moe_plan(const int* ids, int P, int E, int* rank, int* perm, int* tile_e, int* tile_row0, int* tile_rows,
@@ -308,11 +403,12 @@ extern "C" int tb_moe_plan(const int* ids, int P, int E, int* rank, int* perm, i
 // mode 0: gate-and-up with SwiGLU (N = 2 * ff rows a expert, output [P][ff]); mode 1: down (output float32 [P][N], pair order).
 extern "C" int tb_moe_grouped(const void* X, int ldx, const void* W, void* out, int ldo, int dtype, int mode, const int* perm,
                               const int* tile_e, const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles,
-                              int N, int K, int top, cudaStream_t stream) {
+                              int N, int K, int top, int n_real, int act, float limit, cudaStream_t stream) {
     TB_REQUIRE(N > 0 && K > 0 && top > 0 && max_tiles > 0 && max_tiles <= 65535, "moe_grouped: sizes (N=%d K=%d tiles=%d)", N, K, max_tiles);
+    TB_REQUIRE(act >= 0 && act < TB_ACT_KINDS && n_real > 0, "moe_grouped: unknown gate %d or no expert", act);
     TB_REQUIRE(mode == 1 || N % 2 == 0, "moe_grouped: gate and up rows come in pairs");
     dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
-#define MOE_G(TT, MM) tb_launch(moe_grouped_kernel<TT, MM>, grid, 256, 0, stream, (const TT*)X, ldx, (const TT*)W, out, ldo, perm, tile_e, tile_row0, tile_rows, n_tiles, N, K, top)
+#define MOE_G(TT, MM) tb_launch(moe_grouped_kernel<TT, MM>, grid, 256, 0, stream, (const TT*)X, ldx, (const TT*)W, out, ldo, perm, tile_e, tile_row0, tile_rows, n_tiles, N, K, top, n_real, act, limit)
     if (dtype == TB_F32) { if (mode == 0) MOE_G(float, 0); else MOE_G(float, 1); }
     else if (dtype == TB_BF16) { if (mode == 0) MOE_G(__nv_bfloat16, 0); else MOE_G(__nv_bfloat16, 1); }
     else TB_REQUIRE(false, "moe_grouped: unknown dtype %d", dtype);
@@ -323,10 +419,11 @@ extern "C" int tb_moe_grouped(const void* X, int ldx, const void* W, void* out, 
 
 // mode 0: N_out = ff (W holds 2 * ff interleaved rows an expert); mode 1: N_out = rows of the down matrix.
 extern "C" int tb_moe_rows(const void* X, int ldx, const void* W, void* out, int ldo, int dtype, int mode, const int* ids,
-                           int P, int N_out, int K, int top, cudaStream_t stream) {
+                           int P, int N_out, int K, int top, int n_real, int act, float limit, cudaStream_t stream) {
     TB_REQUIRE(P > 0 && N_out > 0 && K > 0 && top > 0 && (N_out + 7) / 8 <= 65535, "moe_rows: sizes (P=%d N=%d K=%d)", P, N_out, K);
+    TB_REQUIRE(act >= 0 && act < TB_ACT_KINDS && n_real > 0, "moe_rows: unknown gate %d or no expert", act);
     dim3 grid(P, (N_out + 7) / 8);
-#define MOE_R(TT, MM) tb_launch(moe_rows_kernel<TT, MM>, grid, 256, 0, stream, (const TT*)X, ldx, (const TT*)W, out, ldo, ids, N_out, K, top)
+#define MOE_R(TT, MM) tb_launch(moe_rows_kernel<TT, MM>, grid, 256, 0, stream, (const TT*)X, ldx, (const TT*)W, out, ldo, ids, N_out, K, top, n_real, act, limit)
     if (dtype == TB_F32) { if (mode == 0) MOE_R(float, 0); else MOE_R(float, 1); }
     else if (dtype == TB_BF16) { if (mode == 0) MOE_R(__nv_bfloat16, 0); else MOE_R(__nv_bfloat16, 1); }
     else TB_REQUIRE(false, "moe_rows: unknown dtype %d", dtype);
@@ -345,10 +442,18 @@ extern "C" int tb_moe_gather(const void* x, int ldx, const int* perm, int top, v
 }
 
 // ``where`` (may be null): row of y that holds pair p, if y is not in pair order.
+// ids, n_real, x (rows of ``x_dtype``, stride ldx): pairs of experts from n_real on add the token's input row instead of a
+// row of y (all null / zero: every pair has a row).
 extern "C" int tb_moe_combine(const float* y, const float* wts, const float* shared_y, const float* gate, float* out, int T_,
-                              int H, int top, const int* where, cudaStream_t stream) {
+                              int H, int top, const int* where, const int* ids, int n_real, const void* x, int ldx, int x_dtype,
+                              cudaStream_t stream) {
     TB_REQUIRE(T_ > 0 && H > 0 && top > 0 && y && wts && out, "moe_combine: sizes must be positive");
-    tb_launch(moe_combine_kernel, T_, H >= 1024 ? 256 : 128, 0, stream, y, wts, shared_y, gate, out, H, top, where);
+    TB_REQUIRE(!ids || (x && ldx >= H && n_real > 0), "moe_combine: experts without matrices need the tokens' input rows");
+    const int threads = H >= 1024 ? 256 : 128;
+    if (ids && x_dtype == TB_BF16)
+        tb_launch(moe_combine_kernel<__nv_bfloat16>, T_, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const __nv_bfloat16*)x, ldx);
+    else
+        tb_launch(moe_combine_kernel<float>, T_, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const float*)x, ldx);
     TB_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -37,4 +37,14 @@ struct QkArgs {
     // product): row t is first multiplied by 1/sqrt(sum_z row_sumsq[z][t] / row_width + row_eps), the row_parts partial
     // sums [part][32] added in the order of the parts.  Null: the rows are as they should be.
     const float* row_sumsq; int row_parts; int row_width; float row_eps;
+    // A unit norm of every Q and K head, with or without a weight: norm_dims > 0 divides a head by the root mean square over
+    // its first norm_dims elements (heads padded with zeros beyond them keep their mean), multiplied by q_w / k_w where given.
+    // norm_after: the mean is taken over the rotated head (after the rotation) instead of before it.
+    int norm_dims; int norm_after;
+    // Values blended across layers: V head rows become (1 - *v_mix) v + *v_mix v_first[t] before they go anywhere
+    // (v_first: rows [T][v_first_stride] of the output dtype, the kv heads side by side; null: no blending).  v_keep
+    // (null: nowhere) receives the V rows as they go to the cache, [T][v_keep_stride] in the output dtype: the place a later
+    // layer blends with, or the step's own V columns, which the prompt kernels read.
+    const void* v_first; int v_first_stride; const float* v_mix;
+    void* v_keep; int v_keep_stride;
 };

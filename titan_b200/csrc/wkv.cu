@@ -1,0 +1,256 @@
+// The "wkv" mixer: a linear recurrence whose decay is made from the token itself, with a bonus for the current token.
+//
+//   mix_s[t] = h[t] + (h[t-1] - h[t]) * mu_s        s in r, k, v, g, w; h[-1] is the last row of the step before (zero at the start)
+//   w[t]     = exp(-exp(W2 tanh(W1 mix_w[t]) + w0))  per head and key channel, float32
+//   o[t]     = (S + diag(u) k[t] v[t]^T)^T r[t]      per head; S: [dk][dk] float32 (key x value)
+//   S        = diag(w[t]) S + k[t] v[t]^T
+//   y[t]     = o[t] / rms(o[t]) per head, * weight * silu(g[t])
+//
+// A sequence's state (every head's S, then the last input row) lies in one float32 row of the cache's state group.  The
+// projections r, k, v, g and W1 mix_w are matrix products of the compute dtype; everything that enters the recurrence
+// after them is float32 here: the decay and its two exponentials, the bonus, the state, the sums and the unit norm.
+//
+//   tb_wkv_shift   the five mixes of every token, side by side in one row (a block a token)
+//   tb_wkv_decay   w of every token and channel from the low-rank product's first half (tanh, the second product, w0, exp(-exp))
+//   tb_wkv_scan    the recurrence; grid (sequences, heads, ceil(dk / 32)): a block owns 32 value columns of one head's state,
+//                  four neighbouring lanes share a column (a quarter of its rows each, in registers) and add their parts of
+//                  o by two shuffles; tokens are staged in shared memory a chunk at a time, the next chunk's loads in
+//                  flight while this one is worked through.  Tokens are taken in order whatever the step brings, so a
+//                  prompt run whole, in pieces or token by token leaves the same state.  The block of head 0 also
+//                  leaves the sequence's last input row in the state.
+//   tb_wkv_out     unit RMS of every head's o, the weight and the gate (a warp a token and head)
+#include "common.cuh"
+
+struct WkvArgs {
+    const void* h; int h_stride;            // [T][h_stride] the mixer's input rows (compute dtype), W wide
+    void* mixes; int mix_stride;            // [T][mix_stride]: mix_r | mix_k | mix_v | mix_g | mix_w, each W wide (compute dtype)
+    const float* mu;                        // [5][W]
+    const void* proj; int proj_stride;      // [T][proj_stride]: r | k | v | g, each H * dk wide (compute dtype)
+    const void* lora; int lora_stride;      // [T][lora_stride]: W1 mix_w, rank wide (compute dtype)
+    const void* w2;                         // [H * dk][rank] (compute dtype)
+    const float* w0;                        // [H * dk]
+    float* decay;                           // [T][H * dk] float32
+    const float* u;                         // [H][dk]
+    float* out; int out_stride;             // [T][out_stride] float32: head h at h * dk
+    float* state; long long state_stride;   // [slots][state_stride]: S [H][dk][dk], then the last input row [W]
+    const float* norm_w;                    // [H * dk]
+    void* y; int y_stride;                  // [T][y_stride] (compute dtype)
+    float eps;
+    const int* q_start; const int* slot_of_seq; const int* seq_of;
+    int T; int B; int H; int dk; int W; int rank; int max_new;
+};
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) wkv_shift_kernel(WkvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, seq = a.seq_of[t];
+    const bool first = t == a.q_start[seq];
+    const T* cur = (const T*)a.h + (size_t)t * a.h_stride;
+    const T* before = cur - a.h_stride;
+    const float* last = a.state + (size_t)a.slot_of_seq[seq] * a.state_stride + (size_t)a.H * a.dk * a.dk;
+    T* out = (T*)a.mixes + (size_t)t * a.mix_stride;
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+        const float x = ldf(cur + i), p = first ? last[i] : ldf(before + i);
+#pragma unroll
+        for (int s = 0; s < 5; ++s) stf(out + (size_t)s * a.W + i, x + (p - x) * a.mu[(size_t)s * a.W + i]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) wkv_decay_kernel(WkvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float th[];           // tanh of the token's low-rank row
+    const int t = blockIdx.x, N = a.H * a.dk;
+    const T* row = (const T*)a.lora + (size_t)t * a.lora_stride;
+    for (int j = threadIdx.x; j < a.rank; j += blockDim.x) th[j] = tanhf(ldf(row + j));
+    __syncthreads();
+    const int n = blockIdx.y * 128 + threadIdx.x;
+    if (n >= N) return;
+    const T* w = (const T*)a.w2 + (size_t)n * a.rank;
+    float z = 0.f;
+    for (int j = 0; j < a.rank; ++j) z = fmaf(ldf(w + j), th[j], z);
+    a.decay[(size_t)t * N + n] = expf(-expf(z + a.w0[n]));
+}
+
+template <typename T, int R, int CH>
+__global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DKP = 4 * (R + 4);                    // a row of dk numbers in shared memory: four runs of R, each padded by 4
+    constexpr int ROW = 4 * DKP + 32;                   // r | k | w | r * u | 32 values
+    constexpr int PER = (CH * (12 * R + 32) + 127) / 128;
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, s = tid & 3, col = tid >> 2, j = blockIdx.z * 32 + col;
+    const int dk = a.dk, N = a.H * dk;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    const bool live = j < dk;
+    float* slot_state = a.state + (size_t)a.slot_of_seq[b] * a.state_stride;
+    float* S_g = slot_state + ((size_t)h * dk) * dk + j;
+    float S[R];
+#pragma unroll
+    for (int ii = 0; ii < R; ++ii) {
+        const int i = s * R + ii;
+        S[ii] = (live && i < dk) ? S_g[(size_t)i * dk] : 0.f;
+    }
+    const T* proj = (const T*)a.proj;
+    const float* bonus = a.u + (size_t)h * dk;
+    const int per_tok = 3 * dk + 32, total = CH * per_tok;
+    // Element e of a chunk: token e / per_tok, then r, k, w (dk each) and the block's 32 values.  ``fetch`` reads it from a
+    // valid address in every case (indices are clamped, so the load carries no condition); ``place`` says where it goes in
+    // shared memory, whether it is real, and which key channel it belongs to (r only: its product with the bonus goes
+    // DKP * 3 further on).
+    auto fetch = [&](int u, int first) -> float {
+        const int e = min(tid + 128 * u, total - 1), tok = e / per_tok, x = e % per_tok;
+        const size_t row = (size_t)min(first + tok, t1 - 1);
+        if (x < 3 * dk) {
+            const int arr = x / dk, i = x - arr * dk;
+            if (arr == 2) return a.decay[row * N + h * dk + i];
+            return ldf(proj + row * a.proj_stride + (size_t)arr * N + h * dk + i);
+        }
+        const int c = min(blockIdx.z * 32 + (x - 3 * dk), dk - 1);
+        return ldf(proj + row * a.proj_stride + (size_t)2 * N + h * dk + c);
+    };
+    auto place = [&](int u, int first, int* to, int* channel) -> bool {
+        const int e = tid + 128 * u, ec = min(e, total - 1), tok = ec / per_tok, x = ec % per_tok;
+        bool ok = e < total && first + tok < t1;
+        *channel = -1;
+        if (x < 3 * dk) {
+            const int arr = x / dk, i = x - arr * dk;
+            *to = tok * ROW + arr * DKP + (i / R) * (R + 4) + (i % R);
+            if (arr == 0) *channel = i;
+            return ok;
+        }
+        const int c = x - 3 * dk;
+        *to = tok * ROW + 4 * DKP + c;
+        return ok && blockIdx.z * 32 + c < dk;
+    };
+    float stage[PER];
+    for (int e = tid; e < CH * ROW; e += 128) sm[e] = 0.f;       // the padding between runs and rows beyond dk are factors: zero
+    if (t0 < t1) {
+#pragma unroll
+        for (int u = 0; u < PER; ++u) stage[u] = fetch(u, t0);
+    }
+    for (int c0 = t0; c0 < t1; c0 += CH) {
+        __syncthreads();                                // the chunk before has been read (or the zeros are in place)
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            if (tid + 128 * u < total) {
+                int to, channel;
+                const bool real = place(u, c0, &to, &channel);
+                const float v = real ? stage[u] : 0.f;
+                sm[to] = v;
+                if (channel >= 0) sm[to + 3 * DKP] = v * bonus[channel];
+            }
+        }
+        __syncthreads();
+        if (c0 + CH < t1) {
+#pragma unroll
+            for (int u = 0; u < PER; ++u) stage[u] = fetch(u, c0 + CH);
+        }
+        const int n = min(CH, t1 - c0);
+        for (int tt = 0; tt < n; ++tt) {
+            const float* rs = sm + tt * ROW + s * (R + 4);
+            const float* ks = rs + DKP;
+            const float* ws = ks + DKP;
+            const float* us = ws + DKP;
+            const float vj = sm[tt * ROW + 4 * DKP + col];
+            float acc = 0.f, now = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < R; ii += 4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rs + ii), k4 = *reinterpret_cast<const float4*>(ks + ii);
+                const float4 w4 = *reinterpret_cast<const float4*>(ws + ii), u4 = *reinterpret_cast<const float4*>(us + ii);
+                acc = fmaf(S[ii], r4.x, acc);     now = fmaf(u4.x, k4.x, now); S[ii] = fmaf(w4.x, S[ii], k4.x * vj);
+                acc = fmaf(S[ii + 1], r4.y, acc); now = fmaf(u4.y, k4.y, now); S[ii + 1] = fmaf(w4.y, S[ii + 1], k4.y * vj);
+                acc = fmaf(S[ii + 2], r4.z, acc); now = fmaf(u4.z, k4.z, now); S[ii + 2] = fmaf(w4.z, S[ii + 2], k4.z * vj);
+                acc = fmaf(S[ii + 3], r4.w, acc); now = fmaf(u4.w, k4.w, now); S[ii + 3] = fmaf(w4.w, S[ii + 3], k4.w * vj);
+            }
+            acc = fmaf(now, vj, acc);                   // the current token's own pair, weighted by the bonus
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + h * dk + j] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < R; ++ii) {
+            const int i = s * R + ii;
+            if (i < dk) S_g[(size_t)i * dk] = S[ii];
+        }
+    }
+    if (h == 0 && blockIdx.z == 0 && t0 < t1) {         // the row that the next step's first token is mixed with
+        float* last = slot_state + (size_t)a.H * dk * dk;
+        const T* row = (const T*)a.h + (size_t)(t1 - 1) * a.h_stride;
+        for (int i = tid; i < a.W; i += 128) last[i] = ldf(row + i);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) wkv_out_kernel(WkvArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x, h = blockIdx.y * 4 + warp;
+    if (h >= a.H) return;
+    const int dk = a.dk, N = a.H * dk;
+    const float* o = a.out + (size_t)t * a.out_stride + h * dk;
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += o[i] * o[i];
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)dk + a.eps);
+    const T* g = (const T*)a.proj + (size_t)t * a.proj_stride + (size_t)3 * N + h * dk;
+    T* y = (T*)a.y + (size_t)t * a.y_stride + h * dk;
+    for (int i = lane; i < dk; i += 32) {
+        const float gv = ldf(g + i);
+        stf(y + i, o[i] * scale * a.norm_w[h * dk + i] * (gv / (1.0f + expf(-gv))));
+    }
+}
+
+template <typename T, int R, int CH>
+cudaError_t launch_scan(const WkvArgs& a, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)CH * (4 * 4 * (R + 4) + 32) * sizeof(float);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        cudaFuncSetAttribute(wkv_scan_kernel<T, R, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        raised = true;
+    }
+    return tb_launch(wkv_scan_kernel<T, R, CH>, dim3(a.B, a.H, (a.dk + 31) / 32), 128, smem, stream, a);
+}
+
+template <typename T>
+int run(const WkvArgs& a, int stage, cudaStream_t stream) {
+    if (stage == 0) tb_launch(wkv_shift_kernel<T>, a.T, 256, 0, stream, a);
+    else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3(a.T, (a.H * a.dk + 127) / 128), 128, (size_t)a.rank * sizeof(float), stream, a);
+    else if (stage == 2) {
+        if (a.dk <= 32) launch_scan<T, 8, 16>(a, stream);
+        else if (a.dk <= 64) launch_scan<T, 16, 16>(a, stream);
+        else if (a.dk <= 128) launch_scan<T, 32, 16>(a, stream);
+        else launch_scan<T, 64, 8>(a, stream);
+    } else tb_launch(wkv_out_kernel<T>, dim3(a.T, (a.H + 3) / 4), 128, 0, stream, a);
+    return 0;
+}
+
+}  // namespace
+
+// stage 0: the mixes; 1: the decay; 2: the recurrence; 3: unit norm, weight and gate.
+extern "C" int tb_wkv(const WkvArgs* args, int stage, int dtype, cudaStream_t stream) {
+    WkvArgs a = *args;
+    TB_REQUIRE(stage >= 0 && stage <= 3, "wkv: unknown stage %d", stage);
+    TB_REQUIRE(a.T > 0 && a.B > 0 && a.H > 0 && a.dk > 0 && a.W > 0, "wkv: sizes must be positive");
+    TB_REQUIRE(a.dk <= 256, "wkv: %d key channels a head (at most 256)", a.dk);
+    TB_REQUIRE(a.H <= 65535 && a.T <= 2147483647, "wkv: too many heads");
+    TB_REQUIRE(a.state && a.state_stride >= (long long)a.H * a.dk * a.dk + a.W, "wkv: the state row is shorter than the heads' states and an input row");
+    TB_REQUIRE(stage != 0 || (a.h && a.mixes && a.mu && a.seq_of && a.q_start && a.slot_of_seq), "wkv: the mixes need rows, factors and the layout");
+    TB_REQUIRE(stage != 1 || (a.lora && a.w2 && a.w0 && a.decay && a.rank > 0 && a.rank <= 8192), "wkv: the decay needs its low-rank row and matrices");
+    TB_REQUIRE(stage != 2 || (a.h && a.proj && a.decay && a.u && a.out && a.q_start && a.slot_of_seq), "wkv: the recurrence needs projections, decay, bonus and the layout");
+    TB_REQUIRE(stage != 3 || (a.out && a.proj && a.norm_w && a.y), "wkv: the output step needs sums, gate, weight and a place for the result");
+    if (dtype == TB_F32) run<float>(a, stage, stream);
+    else if (dtype == TB_BF16) run<__nv_bfloat16>(a, stage, stream);
+    else TB_REQUIRE(false, "wkv: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("wkv");
+    return 0;
+}

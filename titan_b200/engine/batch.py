@@ -115,6 +115,7 @@ class StepContext:
 
     sites_taken: int = 0               # places of "row_sums" handed out in this step
     run: int = 0                       # which run of the layer order is at work (set by the model)
+    next_block: object = None          # the block that runs after this one (None after the last): a block may prepare its input
     carried: Dict[object, object] = field(default_factory=dict)     # what parts hand on within THIS step (a cache owner's rows for its readers, ...)
     after_blocks: List[object] = field(default_factory=list)        # callables the model runs once after the last block (appends that had to wait)
 

@@ -83,6 +83,7 @@ class DecoderModel:
             ctx.scratch["row_sums"] = torch.zeros((len(self.spec.order), 16, 32), dtype=torch.float32, device=ctx.device)
         for run, i in enumerate(self.spec.order):
             ctx.run = run
+            ctx.next_block = self.blocks[self.spec.order[run + 1]] if run + 1 < len(self.spec.order) else None
             self.blocks[i].forward(x, ctx, cache.view_for_layer(self.cache_run_of(run)))
         for late in ctx.after_blocks:          # cache rows that a later layer of the step still had to read as they were
             late()

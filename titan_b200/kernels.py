@@ -18,6 +18,10 @@ from .csrc import build as _build
 
 EPI_STORE, EPI_F32, EPI_ADD, EPI_SWIGLU = 0, 1, 2, 3
 F32, BF16 = 0, 1
+# What the SWIGLU epilogue makes of a (gate, up) pair of sums (csrc/activation.h): silu(g) u; gelu_tanh(g) u; or, with
+# g' = min(g, limit) and u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+ACT_SILU, ACT_GELU_TANH, ACT_SWISH_CLAMPED = 0, 1, 2
+GATES = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "swish_clamped": ACT_SWISH_CLAMPED}
 
 launch_count = 0          # launcher calls since import (a launcher starts one or two kernels)
 _launch_log = None        # while a log is open: launcher name -> calls (berniehans/titan keeps such a record per launch, engine-cuda/src/dispatch_telemetry.rs:13-143)
@@ -72,7 +76,9 @@ class QkArgs(Structure):
                 ("rope", RotaryArgs), ("eps", c_float), ("nh", c_int), ("nkv", c_int),
                 ("hd", c_int), ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p),
                 ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int), ("kv_len", c_void_p),
-                ("row_sumsq", c_void_p), ("row_parts", c_int), ("row_width", c_int), ("row_eps", c_float)]
+                ("row_sumsq", c_void_p), ("row_parts", c_int), ("row_width", c_int), ("row_eps", c_float),
+                ("norm_dims", c_int), ("norm_after", c_int),
+                ("v_first", c_void_p), ("v_first_stride", c_int), ("v_mix", c_void_p), ("v_keep", c_void_p), ("v_keep_stride", c_int)]
 
 
 class AttnArgs(Structure):
@@ -81,7 +87,7 @@ class AttnArgs(Structure):
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
                 ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs)),
-                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int)]
+                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int), ("sink", c_void_p)]
 
 
 class LatentArgs(Structure):
@@ -108,6 +114,16 @@ class LightningArgs(Structure):
                 ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int), ("max_new", c_int)]
 
 
+class WkvArgs(Structure):
+    """Arguments of the wkv mixer's kernels (csrc/wkv.cu)."""
+    _fields_ = [("h", c_void_p), ("h_stride", c_int), ("mixes", c_void_p), ("mix_stride", c_int), ("mu", c_void_p),
+                ("proj", c_void_p), ("proj_stride", c_int), ("lora", c_void_p), ("lora_stride", c_int), ("w2", c_void_p),
+                ("w0", c_void_p), ("decay", c_void_p), ("u", c_void_p), ("out", c_void_p), ("out_stride", c_int),
+                ("state", c_void_p), ("state_stride", c_longlong), ("norm_w", c_void_p), ("y", c_void_p), ("y_stride", c_int),
+                ("eps", c_float), ("q_start", c_void_p), ("slot_of_seq", c_void_p), ("seq_of", c_void_p),
+                ("T", c_int), ("B", c_int), ("H", c_int), ("dk", c_int), ("W", c_int), ("rank", c_int), ("max_new", c_int)]
+
+
 class SampleArgs(Structure):
     _fields_ = [("logits", c_void_p), ("ld", c_int), ("V", c_int), ("B", c_int), ("slot_of_row", c_void_p),
                 ("temperature", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p), ("penalty", c_void_p),
@@ -132,6 +148,12 @@ def lib():
         l.tb_scale_f32.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_simt_gated.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_longlong, c_longlong, c_longlong, c_int, c_float, c_void_p]
+        l.tb_dyt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+        l.tb_scale_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        l.tb_wkv.argtypes = [POINTER(WkvArgs), c_int, c_int, c_void_p]
+        l.tb_moe_route_all.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_longlong, c_longlong, c_longlong, c_void_p]
         l.tb_gemm_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
@@ -148,9 +170,11 @@ def lib():
         l.tb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
         l.tb_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_moe_grouped.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_moe_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        l.tb_moe_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_float, c_void_p]
+        l.tb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
@@ -173,9 +197,11 @@ def tlib():
         lib()
         l = _build.load("tensor")
         l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_tc_gated.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_tc_normed.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         l.tb_gemm_tc_normed_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
-        l.tb_gemm_tc_expert_runs.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_tc_expert_runs.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                             c_int, c_float, c_void_p]
         l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         _tlib = l
     return _tlib
@@ -271,15 +297,16 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, eps: float, strea
                             x.shape[-1], eps, stream))
 
 
-def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int) -> None:
-    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T; x and out may be row-strided views."""
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, gate: int = ACT_SILU, limit: float = 0.0) -> None:
+    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T; x and out may be row-strided views.  ``gate``, ``limit``: what the
+    SWIGLU epilogue makes of a pair (ACT_*)."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
-    _check(lib().tb_gemm_simt(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K,
-                              x.stride(0), out.stride(0), epi, stream))
+    _check(lib().tb_gemm_simt_gated(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K,
+                                    x.stride(0), out.stride(0), epi, 1, 0, 0, 0, int(gate), float(limit), stream))
 
 
 def gemm_simt_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, batch: int,
@@ -320,6 +347,47 @@ def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, x: torch.Tensor, eps: float, s
         raise KernelError("rmsnorm_add: contiguous float32 rows of one shape are wanted")
     _check(lib().tb_rmsnorm_add(y.data_ptr(), w.data_ptr(), x.data_ptr(), _ptr(lowp), dtype_code(lowp.dtype) if lowp is not None else F32,
                                 x.shape[0], x.shape[1], eps, int(zero_y), stream))
+
+
+def dyt(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor, y: torch.Tensor, stream: int,
+        rows: Optional[torch.Tensor] = None) -> None:
+    """y[r] = tanh(alpha * x[rows[r] or r]) * w + b: a norm that takes no statistics (x float32 rows, alpha one number on
+    the device, y in its own dtype)."""
+    _need_cuda(x, w, b, alpha, y, rows)
+    if x.dtype != torch.float32 or not (x.is_contiguous() and y.is_contiguous()) or any(t.dtype != torch.float32 for t in (w, b, alpha)):
+        raise KernelError("dyt: contiguous float32 rows in, float32 weight, bias and factor")
+    _check(lib().tb_dyt(x.data_ptr(), w.data_ptr(), b.data_ptr(), alpha.data_ptr(), y.data_ptr(), dtype_code(y.dtype), _ptr(rows), y.shape[0],
+                        x.shape[-1], stream))
+
+
+def scale_add(y: torch.Tensor, scale: Optional[torch.Tensor], x: torch.Tensor, stream: int, zero_y: bool = True, norm=None,
+              h: Optional[torch.Tensor] = None) -> None:
+    """x += y * scale (float32 rows; ``scale`` a vector or None for 1); ``zero_y`` leaves y zeroed for the next sublayer's
+    products to add into; ``norm`` = (w, b, alpha) with ``h``: h = tanh(alpha x) w + b of the NEW rows, in h's dtype."""
+    _need_cuda(y, scale, x, h)
+    if y.dtype != torch.float32 or x.dtype != torch.float32 or y.shape != x.shape or not (y.is_contiguous() and x.is_contiguous()) \
+            or (h is not None and (h.shape != x.shape or not h.is_contiguous() or norm is None)):
+        raise KernelError("scale_add: contiguous float32 rows of one shape are wanted")
+    w, b, alpha = norm if h is not None else (None, None, None)
+    _check(lib().tb_scale_add(y.data_ptr(), _ptr(scale), x.data_ptr(), int(zero_y), _ptr(w), _ptr(b), _ptr(alpha), _ptr(h),
+                              dtype_code(h.dtype) if h is not None else F32, x.shape[0], x.shape[1], stream))
+
+
+WKV_SHIFT, WKV_DECAY, WKV_SCAN, WKV_OUT = 0, 1, 2, 3
+
+
+def wkv(args: "WkvArgs", stage: int, dtype: torch.dtype, stream: int) -> None:
+    """One of the wkv mixer's four kernels (WKV_SHIFT, WKV_DECAY, WKV_SCAN, WKV_OUT) on the argument block."""
+    _check(lib().tb_wkv(byref(args), int(stage), dtype_code(dtype), stream))
+
+
+def moe_route_all(z: torch.Tensor, top: int, correction: Optional[torch.Tensor], groups: int, keep: int, ids: torch.Tensor,
+                  wts: torch.Tensor, stream: int) -> None:
+    """Per row of z (float32 [T, n_all]): scores = softmax over the whole row; the ``top`` experts with the largest
+    score + correction inside the ``keep`` best of ``groups`` groups of neighbours; weights = their scores over their sum."""
+    _need_cuda(z, correction, ids, wts)
+    _check(lib().tb_moe_route_all(z.data_ptr(), z.stride(0), z.shape[1], top, _ptr(correction), groups, keep, ids.data_ptr(), wts.data_ptr(),
+                                  z.shape[0], stream))
 
 
 def round_rows(x: torch.Tensor, out: torch.Tensor, stream: int) -> None:
@@ -422,30 +490,35 @@ def moe_gather(x: torch.Tensor, plan: MoePlan, top: int, out: torch.Tensor, stre
     _check(lib().tb_moe_gather(x.data_ptr(), x.stride(0), plan.perm.data_ptr(), top, out.data_ptr(), dtype_code(x.dtype), plan.pairs, x.shape[1], stream))
 
 
-def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, plan, top: int, stream: int) -> None:
+def moe_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, plan, top: int, stream: int,
+                gate: int = ACT_SILU, limit: float = 0.0) -> None:
     """The experts' products over the plan's tiles on the CUDA cores.  mode 0: x [T, K] tokens, w [E, 2F, K] (gate and up
     rows interleaved), out [P, F] in sorted order; mode 1: x [P, K] sorted rows, w [E, N, K], out float32 [P, N] in pair order."""
     _need_cuda(x, w, out)
     _check(lib().tb_moe_grouped(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), dtype_code(w.dtype), mode,
                                 plan.perm.data_ptr(), plan.tile_e.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(),
-                                plan.n_tiles.data_ptr(), plan.tiles, w.shape[1], w.shape[2], top, stream))
+                                plan.n_tiles.data_ptr(), plan.tiles, w.shape[1], w.shape[2], top, w.shape[0], int(gate), float(limit), stream))
 
 
-def moe_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ids: torch.Tensor, top: int, stream: int) -> None:
+def moe_rows(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, ids: torch.Tensor, top: int, stream: int,
+             gate: int = ACT_SILU, limit: float = 0.0) -> None:
     """The same two products for a few pairs, a warp per output, without a plan (pair order in and out)."""
     _need_cuda(x, w, out, ids)
     n_out = w.shape[1] // 2 if mode == 0 else w.shape[1]
     _check(lib().tb_moe_rows(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), dtype_code(w.dtype), mode,
-                             ids.data_ptr(), ids.numel(), n_out, w.shape[2], top, stream))
+                             ids.data_ptr(), ids.numel(), n_out, w.shape[2], top, w.shape[0], int(gate), float(limit), stream))
 
 
 def moe_combine(y: torch.Tensor, wts: torch.Tensor, shared_y: Optional[torch.Tensor], gate: Optional[torch.Tensor],
-                out: torch.Tensor, top: int, stream: int, where: Optional[torch.Tensor] = None) -> None:
+                out: torch.Tensor, top: int, stream: int, where: Optional[torch.Tensor] = None,
+                ids: Optional[torch.Tensor] = None, n_real: int = 0, x: Optional[torch.Tensor] = None) -> None:
     """out[t] += sum_k wts[t, k] * y[row of pair t * top + k] (+ gate[t] * shared_y[t]); everything float32.  The row of
-    pair p is p, or ``where[p]`` if y is in another order (a plan's ``inverse``)."""
-    _need_cuda(y, wts, shared_y, gate, out, where)
+    pair p is p, or ``where[p]`` if y is in another order (a plan's ``inverse``).  With ``ids``, ``n_real`` and ``x``: a
+    pair whose expert is ``n_real`` or beyond has no matrices; its output is the token's own input row x[t]."""
+    _need_cuda(y, wts, shared_y, gate, out, where, ids, x)
     _check(lib().tb_moe_combine(y.data_ptr(), wts.data_ptr(), _ptr(shared_y), _ptr(gate), out.data_ptr(), out.shape[0], out.shape[1], top,
-                                _ptr(where), stream))
+                                _ptr(where), _ptr(ids), int(n_real), _ptr(x), x.stride(0) if x is not None else 0,
+                                dtype_code(x.dtype) if x is not None else F32, stream))
 
 
 def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> bool:
@@ -458,7 +531,8 @@ def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: in
                                   x.data_ptr(), w.data_ptr(), out.data_ptr()) == 0
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, splits: int = 0, ordered: bool = False) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, splits: int = 0, ordered: bool = False,
+            gate: int = ACT_SILU, limit: float = 0.0) -> None:
     """out (epilogue ``epi``) = x[M,K] . w[N,K]^T on the tcgen05 tensor cores (bfloat16 operands).  ``ordered``: partial
     sums along K add up in a fixed order (the K slices of a decode product inside a thread-block cluster, no prompt tile
     cut along K), so that the same inputs give the same bits on every run; the default lets float32 reductions meet at
@@ -473,11 +547,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
     N = w.shape[0]
     if w.shape[1] != K_ or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
-    _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
-                            -1 if ordered and not splits else splits, stream))
+    _check(tlib().tb_gemm_tc_gated(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
+                                  -1 if ordered and not splits else splits, int(gate), float(limit), stream))
 
 
-def gemm_tc_expert_runs(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, first, stream: int) -> None:
+def gemm_tc_expert_runs(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor, first, stream: int,
+                        gate: int = ACT_SILU, limit: float = 0.0) -> None:
     """For every run s of rows [first[s], first[s + 1]): act = swiglu(x . w_gate_up[s]^T), y = act . w_down[s]^T (float32), on the
     tensor cores, the runs spread over a few side streams (w_gate_up [E, 2F, H] with gate and up rows interleaved, w_down [E, H, F])."""
     global launch_count
@@ -490,7 +565,7 @@ def gemm_tc_expert_runs(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Ten
     arr = (c_int * len(first))(*first)
     launch_count += 2 * sum(1 for a, b in zip(first, first[1:]) if b > a) - 1
     _check(tlib().tb_gemm_tc_expert_runs(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), act.data_ptr(), act.stride(0), w_down.data_ptr(),
-                                        y.data_ptr(), y.stride(0), arr, E, H, F2 // 2, stream))
+                                        y.data_ptr(), y.stride(0), arr, E, H, F2 // 2, int(gate), float(limit), stream))
 
 
 def gemm_tc_normed_accepts(x: torch.Tensor, norm_w: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,

@@ -20,6 +20,19 @@ which is what makes a ring of ``window`` rows safe.
 
 With ``cache_from`` the mixer owns no keys: it projects queries only and reads
 the named layer's cache.
+
+Options of the spec (``MixerSpec.extra``) beyond the common fields:
+
+* ``value_dim``: width of a value head where it differs from the key's.  Keys and values are stored at one width, the
+  larger of the two rounded up to 16; the narrower one's rows of the projections (and the columns of the output
+  projection) are padded with zeros when the tensors are bound, which changes no score and no output.
+* ``unit_norm`` = "after_rotation" | "before_rotation" with ``unit_norm_eps``: every Q and K head is divided by its
+  root mean square (over the head's own width), without a weight, after or before the rotation.
+* ``sink``: name of a tensor with one number per query head that joins the softmax's denominator as exp(sink), with no
+  key and no value, once.
+* ``value_mix`` = (first, name): values are blended across layers.  ``first`` None: this layer's values are what the
+  others blend with, and it keeps them for the step; else v <- (1 - l) v + l v_first with l the tensor ``name`` and
+  v_first the values of layer ``first`` for the same tokens.  The blended values are what the cache holds.
 """
 from __future__ import annotations
 
@@ -73,19 +86,36 @@ class AttentionMixer(Mixer):
         s = spec
         if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
             raise ValueError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} kv heads")
-        if s.head_dim % 16 or not 16 <= s.head_dim <= 256:
-            raise ValueError(f"head_dim {s.head_dim} is not supported: multiples of 16 from 16 to 256")
+        self.key_dim, self.value_dim = s.head_dim, int(s.option("value_dim", s.head_dim))
+        self.hd = -(-max(self.key_dim, self.value_dim) // 16) * 16          # the one width heads are computed and stored at
+        if self.key_dim <= 0 or self.value_dim <= 0 or self.hd > 256:
+            raise ValueError(f"heads of {self.key_dim} (keys) and {self.value_dim} (values) are not supported: at most 256")
+        self.padded = (self.key_dim, self.value_dim) != (self.hd, self.hd)
+        if self.padded and s.qk_norm is not None:
+            raise ValueError("a head norm with a weight needs heads of a multiple of 16, keys and values of one width")
         if s.window is not None and s.window <= 0:
             raise ValueError("an attention window must be positive")
         if s.cache_from is not None and s.window is not None:
             raise ValueError("a mixer that reads another layer's cache cannot have a window")
         self.spec = s
-        self.Q, self.KV = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        self.Q, self.KV = s.num_heads * self.hd, s.num_kv_heads * self.hd
         self.shared = s.cache_from is not None
+        self.unit_norm = s.option("unit_norm")
+        if self.unit_norm not in (None, "after_rotation", "before_rotation") or (self.unit_norm and s.qk_norm is not None):
+            raise ValueError("unit_norm is 'after_rotation' or 'before_rotation', and takes the place of a head norm with a weight")
+        self.sink_name = s.option("sink")
+        self.value_mix = s.option("value_mix")          # None, or (first layer or None, tensor name)
+        if self.value_mix is not None and self.shared:
+            raise ValueError("a mixer that reads another layer's cache has no values to blend")
+        # what the kernels that fold head norm, rotation and append into the attention do not know
+        self.extended = bool(self.unit_norm or self.value_mix is not None or self.padded)
+        self.sink = self.mix_factor = None
         self.position = POSITIONS.build(s.position)
         if getattr(s.position, "pairing", "half") != "half" and s.position.kind == "rope":
             raise ValueError("grouped-query attention rotates the pairs (k, k + rotary_dim/2) only")
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+        if s.position.kind == "rope" and s.position.rotary_dim > self.key_dim:
+            raise ValueError(f"{s.position.rotary_dim} rotated dimensions in a head of {self.key_dim}")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
         self._views = {}
 
@@ -93,7 +123,7 @@ class AttentionMixer(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         if self.shared:
             return None
-        return CacheNeed("kv", self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        return CacheNeed("kv", self.spec.num_kv_heads, self.hd, self.spec.window)
 
     def _names(self):
         """Tensor names (relative to the prefix) by role; "qkv" only if the spec names a fused tensor."""
@@ -106,14 +136,21 @@ class AttentionMixer(Mixer):
 
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
         s, p, n = self.spec, prefix + self.spec.prefix, self._names()
-        specs = [WeightSpec(p + n["o"], (s.hidden_size, self.Q))]
+        kd, vd = self.key_dim, self.value_dim
+        specs = [WeightSpec(p + n["o"], (s.hidden_size, s.num_heads * vd))]
         if n["qkv"] is not None:
+            if self.padded:
+                raise ValueError("a fused q|k|v tensor needs heads of a multiple of 16, keys and values of one width")
             specs.append(WeightSpec(p + n["qkv"], (self.Q + 2 * self.KV, s.hidden_size)))
         else:
-            specs.append(WeightSpec(p + n["q"], (self.Q, s.hidden_size)))
+            specs.append(WeightSpec(p + n["q"], (s.num_heads * kd, s.hidden_size)))
             if not self.shared:
-                specs += [WeightSpec(p + n["k"], (self.KV, s.hidden_size)),
-                          WeightSpec(p + n["v"], (self.KV, s.hidden_size))]
+                specs += [WeightSpec(p + n["k"], (s.num_kv_heads * kd, s.hidden_size)),
+                          WeightSpec(p + n["v"], (s.num_kv_heads * vd, s.hidden_size))]
+        if self.sink_name:
+            specs.append(WeightSpec(p + self.sink_name, (s.num_heads,), "vector", ("normal", 1.0)))
+        if self.value_mix is not None:
+            specs.append(WeightSpec(p + self.value_mix[1], (), "vector", ("normal", 0.3)))
         if s.qk_norm is not None:
             for which in ("q",) if self.shared else ("q", "k"):
                 specs.append(WeightSpec(p + s.qk_norm.weight.format(which), (s.head_dim,), "vector", ("one_plus_normal", 0.1)))
@@ -124,14 +161,29 @@ class AttentionMixer(Mixer):
         if n["qkv"] is not None:
             self.w_qkv = get(p + n["qkv"])
         else:
-            parts = [get(p + n["q"])]
+            parts = [self._padded_rows(get(p + n["q"]), s.num_heads, self.key_dim)]
             if not self.shared:
-                parts += [get(p + n["k"]), get(p + n["v"])]
+                parts += [self._padded_rows(get(p + n["k"]), s.num_kv_heads, self.key_dim),
+                          self._padded_rows(get(p + n["v"]), s.num_kv_heads, self.value_dim)]
             self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]
         self.w_o = get(p + n["o"])
+        if self.value_dim != self.hd:                 # zero columns where the heads' outputs are padded
+            w = self.w_o.reshape(s.hidden_size, s.num_heads, self.value_dim)
+            self.w_o = torch.nn.functional.pad(w, (0, self.hd - self.value_dim)).reshape(s.hidden_size, self.Q).contiguous()
+        if self.sink_name:
+            self.sink = get(p + self.sink_name)
+        if self.value_mix is not None:
+            self.mix_factor = get(p + self.value_mix[1]).reshape(1)
         if s.qk_norm is not None:
             self.q_norm = get(p + s.qk_norm.weight.format("q"))
             self.k_norm = None if self.shared else get(p + s.qk_norm.weight.format("k"))
+
+    def _padded_rows(self, w: torch.Tensor, heads: int, dim: int) -> torch.Tensor:
+        """A projection whose heads are ``dim`` wide as one whose heads are ``self.hd`` wide, the new rows zero."""
+        if dim == self.hd:
+            return w
+        w = w.reshape(heads, dim, w.shape[1])
+        return torch.nn.functional.pad(w, (0, 0, 0, self.hd - dim)).reshape(heads * self.hd, -1).contiguous()
 
     # -- one step --------------------------------------------------------- #
     def _view(self, cache) -> K.KvView:
@@ -154,7 +206,9 @@ class AttentionMixer(Mixer):
         qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
         qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
         qa.rope = rope                              # the position encoding's block, passed on as it is
-        qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        qa.eps = s.qk_norm.eps if s.qk_norm is not None else float(s.option("unit_norm_eps", 0.0))
+        if self.unit_norm:
+            qa.norm_dims, qa.norm_after = self.key_dim, int(self.unit_norm == "after_rotation")
         qa.nh, qa.nkv, qa.hd = s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         qa.cache, qa.append, qa.T = view, int(append), T
@@ -164,7 +218,7 @@ class AttentionMixer(Mixer):
 
     def forward(self, h, ctx, cache, out: torch.Tensor) -> None:
         s, lay = self.spec, ctx.layout
-        T, Q, KV, hd = lay.T, self.Q, self.KV, s.head_dim
+        T, Q, KV, hd = lay.T, self.Q, self.KV, self.hd
         width = Q if self.shared else Q + 2 * KV
         view = self._view(cache)
         decode = lay.all_single
@@ -209,7 +263,20 @@ class AttentionMixer(Mixer):
         # A decode step whose Q | K | V are float32 sums may leave head norm, rotation and append to the attention
         # kernel itself (one kernel less between the projection and the attention); decided below, where the
         # attention's arguments are known.  Everything else runs the kernel now.
-        folds_head_norm = wide_sum and ctx.options.get("fold_head_norm", True)
+        if self.value_mix is not None:
+            first, _ = self.value_mix
+            if first is None:                                  # the values that later layers blend theirs with, kept for the step
+                kept = ctx.empty((T, KV))
+                qa.v_keep, qa.v_keep_stride = kept.data_ptr(), KV
+                ctx.carried[("values_of", s.option("layer_index"))] = kept
+            else:
+                kept = ctx.carried.get(("values_of", first))
+                if kept is None or kept.shape != (T, KV):
+                    raise RuntimeError(f"the values of layer {first} that this layer blends with were not kept in this step")
+                qa.v_first, qa.v_first_stride, qa.v_mix = kept.data_ptr(), KV, self.mix_factor.data_ptr()
+                if not wide_sum:                               # the step's own V columns are what a prompt's attention reads
+                    qa.v_keep, qa.v_keep_stride = qkv.data_ptr() + (Q + KV) * qkv.element_size(), width
+        folds_head_norm = wide_sum and ctx.options.get("fold_head_norm", True) and not self.extended
         if not folds_head_norm:
             K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
@@ -220,8 +287,10 @@ class AttentionMixer(Mixer):
         aa.cache, aa.batch = view, lay.c_struct()
         aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
         aa.window, aa.scale = s.window or 0, self.scale
+        aa.sink = None if self.sink is None else self.sink.data_ptr()
         if decode:
-            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
+            fast = (ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
+                    and self.sink is None)               # (the tensor-core kernels take no sink: not asked, so not compiled either)
             chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
@@ -248,7 +317,7 @@ class AttentionMixer(Mixer):
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * qkv.element_size(), width
-            mode = ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
+            mode = ctx.options.get("attention", "fast") if self.sink is None else "plain"   # "fast" | "mma" | "plain"
             # The tensor-core kernels read keys and values from the step's own rows when every sequence starts at
             # position 0, and else from the cache's pages, if the step's keys lie there already (a cache that keeps
             # everything; a reader of another layer's cache finds them there in any case).

@@ -58,6 +58,77 @@ class PreNormBlock(Part):
 BLOCKS.register("pre_norm", PreNormBlock)
 
 
+class ScaledPreNormBlock(Part):
+    """``pre_norm_scaled``: pre-norm with a learned scale on every sublayer's output ("layer scale"):
+
+        x += s1 * mixer(norm1(x));   x += s2 * feed_forward(norm2(x))
+
+    s1 and s2 are vectors as wide as the residual stream, named in ``LayerSpec.extra`` under "scales" (two tensor names
+    relative to the layer's prefix).  The feed-forward, with its norm and scale, may be absent.  A sublayer adds into a
+    zeroed float32 buffer of the step; one kernel then scales that buffer, adds it to the residual stream and leaves it
+    zeroed.  Where the norm that follows is a ``dyt`` norm (its result depends on the element alone), the same kernel
+    also writes the normed rows that the next sublayer reads: the feed-forward's input here, or the next block's
+    mixer input, which the next block then finds in ``ctx.carried`` (the model names the block that runs next)."""
+
+    def __init__(self, spec):
+        if spec.mixer_norm is None or (spec.feed_forward is None) != (spec.feed_forward_norm is None) or spec.norms:
+            raise ValueError("the pre_norm_scaled arrangement takes a mixer with its norm, and a feed-forward with its norm or neither")
+        names = tuple(spec.option("scales", ()))
+        if len(names) != (1 if spec.feed_forward is None else 2):
+            raise ValueError("the pre_norm_scaled arrangement needs the name of one scale vector for each sublayer")
+        self.spec, self.scale_names = spec, names
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.feed_forward_norm = None if spec.feed_forward_norm is None else NORMS.build(spec.feed_forward_norm)
+        self.feed_forward = None if spec.feed_forward is None else FEED_FORWARDS.build(spec.feed_forward)
+        self.scales: List[torch.Tensor] = []
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer) + (() if self.feed_forward is None else (self.feed_forward_norm, self.feed_forward))
+
+    def weight_specs(self, prefix: str = "") -> List[WeightSpec]:
+        out: List[WeightSpec] = []
+        for part in self.parts():
+            out += part.weight_specs(self.spec.prefix)
+        width = self.spec.mixer.hidden_size
+        return out + [WeightSpec(self.spec.prefix + n, (width,), "vector", ("one_plus_normal", 0.1)) for n in self.scale_names]
+
+    def bind(self, get) -> None:
+        for part in self.parts():
+            part.bind(lambda name: get(self.spec.prefix + name))
+        self.scales = [get(self.spec.prefix + n) for n in self.scale_names]
+
+    def _join(self, y, scale, x, ctx, next_norm):
+        """x += scale * y, y zeroed; the rows of ``next_norm`` over the new x if that norm can ride along, else None."""
+        from .. import kernels as K
+        if next_norm is not None and hasattr(next_norm, "triple") and ctx.options.get("fuse_scaled_norm", True):
+            h = ctx.empty(tuple(x.shape))
+            K.scale_add(y, scale, x, ctx.stream, zero_y=True, norm=next_norm.triple(), h=h)
+            return h
+        K.scale_add(y, scale, x, ctx.stream, zero_y=True)
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        y = ctx.carried.get("sublayer_sum")
+        if y is None or y.shape != x.shape:
+            y = ctx.carried["sublayer_sum"] = torch.zeros_like(x)         # zeroed once a step; the joining kernel leaves it zeroed
+        kept = ctx.carried.pop("normed_rows", None)
+        h = kept[0] if kept is not None and kept[1] == ctx.run and kept[0].shape == x.shape else self.mixer_norm.forward(x, ctx)
+        self.mixer.forward(h, ctx, cache, y)
+        following = getattr(ctx.next_block, "mixer_norm", None) if isinstance(ctx.next_block, ScaledPreNormBlock) else None
+        if self.feed_forward is None:
+            h = self._join(y, self.scales[0], x, ctx, following)
+        else:
+            h = self._join(y, self.scales[0], x, ctx, self.feed_forward_norm)
+            self.feed_forward.forward(h if h is not None else self.feed_forward_norm.forward(x, ctx), ctx, y)
+            h = self._join(y, self.scales[1], x, ctx, following)
+        if h is not None:
+            ctx.carried["normed_rows"] = (h, ctx.run + 1)
+
+
+BLOCKS.register("pre_norm_scaled", ScaledPreNormBlock)
+
+
 class OutputNormBlock(Part):
     """``output_norm``: every sublayer reads the residual stream itself and its OUTPUT is normed before it is added:
 

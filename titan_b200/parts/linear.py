@@ -20,7 +20,8 @@ EPI_STORE, EPI_F32, EPI_ADD, EPI_SWIGLU = K.EPI_STORE, K.EPI_F32, K.EPI_ADD, K.E
 ROWS_MAX_M, ROWS_MAX_ELEMENTS = 8, 1 << 19
 
 
-def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, ctx) -> None:
+def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, ctx, gate: int = K.ACT_SILU, limit: float = 0.0) -> None:
+    """``gate``, ``limit``: what the SWIGLU epilogue makes of a (gate, up) pair (``kernels.ACT_*``)."""
     if (x.shape[0] <= ROWS_MAX_M and w.shape[0] * w.shape[1] <= ROWS_MAX_ELEMENTS and epi in (EPI_STORE, EPI_F32, EPI_ADD)
             and ctx.options.get("small_products", True)):
         K.gemm_rows(x, w, out, epi, ctx.stream)
@@ -28,9 +29,9 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, ctx) -
     if w.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain":
         fast = getattr(K, "gemm_tc", None)
         if fast is not None and K.gemm_tc_accepts(x, w, out, epi):
-            fast(x, w, out, epi, ctx.stream, ordered=bool(ctx.options.get("reproducible", False)))
+            fast(x, w, out, epi, ctx.stream, ordered=bool(ctx.options.get("reproducible", False)), gate=gate, limit=limit)
             return
-    K.gemm_simt(x, w, out, epi, ctx.stream)
+    K.gemm_simt(x, w, out, epi, ctx.stream, gate, limit)
 
 
 def matmul_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, heads: int, x_step: int, out_step: int, ctx) -> None:

@@ -1,4 +1,5 @@
-"""Gated MLP as a feed-forward: down(act(gate(x)) * up(x)), added into the residual stream.
+"""Gated MLP as a feed-forward: down(act(gate(x)) * up(x)), added into the residual stream; act is silu or the tanh
+form of gelu (``FeedForwardSpec.activation``), applied in the epilogue of the gate-and-up product.
 
 berniehans/titan: engine/engine-core/src/forward_cpu.rs:369-386 with
 silu(g) = g / (1 + exp(-g)) (:210-219); its kernels fuse gate, up and SwiGLU in
@@ -27,8 +28,9 @@ class GatedMLP(FeedForward):
     folds_norm = True           # a decode step's gate-and-up product takes the norm before it in
 
     def __init__(self, spec):
-        if spec.activation != "silu":
-            raise ValueError(f"activation '{spec.activation}' is not supported (only 'silu')")
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"activation '{spec.activation}' is not supported ('silu' or 'gelu_tanh')")
+        self.gate = K.GATES[spec.activation]
         if spec.intermediate_size <= 0:
             raise ValueError("intermediate_size must be positive")
         self.spec = spec
@@ -62,11 +64,11 @@ class GatedMLP(FeedForward):
 
     def forward(self, h, ctx, out: torch.Tensor) -> None:
         act = ctx.empty((h.shape[0], self.spec.intermediate_size))
-        if (isinstance(h, DeferredNorm) and ctx.options.get("gemm", "fast") != "plain" and self.w_gate_up.dtype == torch.bfloat16
+        if (isinstance(h, DeferredNorm) and self.gate == K.ACT_SILU and ctx.options.get("gemm", "fast") != "plain" and self.w_gate_up.dtype == torch.bfloat16
                 and K.gemm_tc_normed_accepts(h.x, h.weight, self.w_gate_up, act, linear.EPI_SWIGLU, None)):
             K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_gate_up, act, linear.EPI_SWIGLU, ctx.stream)
         else:
-            linear.matmul(rows_of(h), self.w_gate_up, act, linear.EPI_SWIGLU, ctx)
+            linear.matmul(rows_of(h), self.w_gate_up, act, linear.EPI_SWIGLU, ctx, gate=self.gate)
         linear.matmul(act, self.w_down, out, linear.EPI_ADD, ctx)
 
 

@@ -60,3 +60,35 @@ class RMSNorm(Norm):
 
 
 NORMS.register("rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Norm):
+    """``dyt``: y = tanh(alpha * x) * w + b, with one learned number alpha: a norm that computes no mean and no variance
+    (``eps`` of the spec is not used).  Tensors: the weight under the spec's name, the bias and alpha beside it as
+    ``<name>.b`` and ``<name>.alpha`` (alpha a tensor without dimensions).  float32 inside.  The block arrangement that
+    scales its sublayers' outputs takes this norm into the kernel that adds them to the residual stream (``triple``)."""
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.weight = self.bias = self.alpha = None
+
+    def weight_specs(self, prefix: str) -> List[WeightSpec]:
+        n = prefix + self.spec.weight
+        return [WeightSpec(n, (self.spec.size,), "vector", ("one_plus_normal", 0.1)), WeightSpec(n + ".b", (self.spec.size,), "vector", ("normal", 0.1)),
+                WeightSpec(n + ".alpha", (), "vector", ("one_plus_normal", 0.1))]
+
+    def bind(self, get) -> None:
+        n = self.spec.weight
+        self.weight, self.bias, self.alpha = get(n), get(n + ".b"), get(n + ".alpha").reshape(1)
+
+    def triple(self):
+        return self.weight, self.bias, self.alpha
+
+    def forward(self, x: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        y = ctx.empty((n, self.spec.size))
+        K.dyt(x, self.weight, self.bias, self.alpha, y, ctx.stream, rows)
+        return y
+
+
+NORMS.register("dyt", DynamicTanh)

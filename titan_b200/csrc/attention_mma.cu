@@ -33,6 +33,15 @@ constexpr int PAGE = 64;
 constexpr int DEC_WARPS = 4;                 // compute warps; warp DEC_WARPS produces
 constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;
 
+// A sink joins a finished softmax (maximum M in units of log2, sum of weights L, unnormalised output acc): against the
+// larger of M and the sink, the old terms shrink by ``keep`` and the sink adds one term to L.  Returns keep / L', the
+// factor on acc.
+__device__ __forceinline__ float sink_factor(const float* sink, int head, float M, float L) {
+    if (!sink) return L > 0.f ? 1.0f / L : 0.f;
+    const float sk = sink[head] * 1.4426950408889634f, top = fmaxf(M, sk), keep = exp2f(M - top);
+    return keep / (L * keep + exp2f(sk - top));
+}
+
 struct DecArgs {
     const __nv_bfloat16* q; int q_stride;    // [B][q_stride]
     float* scratch;                          // [B][nh][n_splits][hd + 2]
@@ -48,6 +57,7 @@ struct DecArgs {
     const float* row_sumsq; int row_parts; int row_width; float row_eps;
     __nv_bfloat16* storage; long long v_half;      // the cache's K half and the distance to its V half, in elements
     int late_trigger;                              // the next kernel may start once this one's pages are read (else: at once)
+    const float* sink;                             // [nh] or null: one more term exp(sink) of every head's softmax denominator
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -415,7 +425,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             L += f * ml[w * 16 + row];
         }
         if (CL && a.n_splits == 1) {      // nothing to merge with: this is the result
-            a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(acc * sink_factor(a.sink, kh * group + row, M, L));
         } else if (CL) {
             // to the CTA that merges this element, into the row of this split; a row's maximum and sum of weights to all
             const int owner = idx / merge_per, e = idx - owner * merge_per;
@@ -467,7 +477,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
                     acc += f * vr[r];
                     L += f * lr[r];
                 }
-                a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+                a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(acc * sink_factor(a.sink, kh * group + row, M, L));
             }
         }
     }
@@ -490,6 +500,7 @@ struct PreArgs {
     // keys and values from the cache: first position of each sequence's rows, slots, block table, first V row of the map
     int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
     int tail_col0;                           // HDT > 0: first column (in the tail map's rows) of the key dimensions that all heads share
+    const float* sink;                       // [nh] or null: one more term exp(sink) of every head's softmax denominator
 };
 
 // HDK: dimensions of a query and of a key; HDV: of a value and of an output row (the same for grouped-query attention).
@@ -646,7 +657,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
     }
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    const float i0 = a.sink ? sink_factor(a.sink, h, m0, l0) : 1.0f / l0, i1 = a.sink ? sink_factor(a.sink, h, m1, l1) : 1.0f / l1;
     __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qr0) * a.out_stride + h * HDV + 2 * t;
     __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qr1) * a.out_stride + h * HDV + 2 * t;
 #pragma unroll
@@ -734,7 +745,6 @@ extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 :
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
     TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
-    TB_REQUIRE(!a->sink, "attn_decode_mma: a softmax with a sink is not taken here");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
     TB_REQUIRE(a->cache.page_size == PAGE, "attn_decode_mma: pages of %d rows, not %d", PAGE, a->cache.page_size);
@@ -776,7 +786,7 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     d.early_len = a.early_len; d.early_mode = a.early_len ? a.early_mode : 0;
     TB_REQUIRE(d.early_mode >= 0 && d.early_mode <= 2, "attn_decode_mma: early_mode %d (0, 1 or 2)", d.early_mode);
     d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
-    d.chunk = a.chunk; d.n_splits = a.n_splits;
+    d.chunk = a.chunk; d.n_splits = a.n_splits; d.sink = a.sink;
     d.out = (__nv_bfloat16*)a.out; d.out_stride = a.out_stride;
     d.acc = nullptr; d.acc_stride = 0; d.q_w = d.k_w = nullptr; d.qk_eps = 0.f; d.rope = TbRotary{nullptr, 0, 0.f, 1.f};
     d.row_sumsq = nullptr; d.row_parts = 0; d.row_width = 1; d.row_eps = 0.f; d.storage = nullptr; d.v_half = 0;
@@ -825,7 +835,6 @@ static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, con
 // and values from the pages of a cache that keeps every key, the step's own appended already).
 extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int source) {
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
-    TB_REQUIRE(!a->sink, "attn_prefill_mma: a softmax with a sink is not taken here");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
@@ -857,7 +866,7 @@ extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int source, cudaStream_
     p.v_row0 = a.cache.num_pages * a.nkv * PAGE;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd; p.tail_col0 = 0;
+    p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd; p.tail_col0 = 0; p.sink = a.sink;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
     TB_REQUIRE(blocks <= 65535, "attn_prefill_mma: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);
@@ -905,7 +914,7 @@ extern "C" int tb_attn_prefill_split(const SplitAttnArgs* args, cudaStream_t str
     p.paged = 0; p.start_pos = nullptr; p.slot_of_seq = nullptr; p.table = nullptr; p.table_width = 0; p.v_row0 = 0;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nh; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.k_col0 = a.k_col0; p.v_col0 = a.v_col0; p.tail_col0 = a.tail_col0;
+    p.k_col0 = a.k_col0; p.v_col0 = a.v_col0; p.tail_col0 = a.tail_col0; p.sink = nullptr;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;
     TB_REQUIRE(blocks <= 65535, "attn_prefill_split: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);

@@ -61,6 +61,7 @@ struct TcAttnArgs {
     // keys and values from the cache (continuation steps): the first position of each sequence's rows, its slot,
     // the block table, and the row of the first V page in the cache's tensor map; paged = 0: from the step's rows
     int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
+    const float* sink;       // [nh] or null: one more term exp(sink) of every head's softmax denominator, without key or value
 };
 
 __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, unsigned code) {
@@ -320,9 +321,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         asm volatile("bar.sync 1, 256;" ::: "memory");           // all eight softmax warps
         tc_fence_after();
         const float m0 = ml_sh[0 * 128 + row], l0 = ml_sh[1 * 128 + row], m1 = ml_sh[2 * 128 + row], l1 = ml_sh[3 * 128 + row];
-        const float M = fmaxf(m0, m1);
+        const float sk = a.sink ? a.sink[h] * 1.4426950408889634f : -1e30f;      // the sink, in units of log2 like the maxima
+        const float M = fmaxf(fmaxf(m0, m1), sk);
         const float w0 = ex2(m0 - M), w1 = n_tiles > 1 ? ex2(m1 - M) : 0.f;
-        const float inv = 1.0f / (l0 * w0 + l1 * w1);
+        const float inv = 1.0f / (l0 * w0 + l1 * w1 + (a.sink ? ex2(sk - M) : 0.f));
         // this thread: output dims 64 g .. 64 g + 63 of its row, from both groups' O
         float o0[64], o1[64];
         tmem_ld32_nowait(tmem_o + lane_addr + g * 64, o0);
@@ -364,7 +366,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 // that keeps every key: no ring).
 extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source) {
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
-    TB_REQUIRE(!a->sink, "attn_prefill_tc: a softmax with a sink is not taken here");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == HD, "attn_prefill_tc: head_dim %d is not %d", a->hd, HD);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
@@ -397,7 +398,7 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int source, cudaStream_t
     p.start_pos = a.batch.start_pos; p.slot_of_seq = a.batch.slot_of_seq; p.table = a.cache.table; p.table_width = a.cache.table_width;
     p.v_row0 = a.cache.num_pages * a.nkv * BKEY;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
-    p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f; p.sink = a.sink;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
     constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 256 + 4 * 128 * sizeof(float);
     static_assert(KV_STAGES == 4, "the second kernel's barrier layout and S buffers assume four stages");

@@ -289,8 +289,7 @@ class AttentionMixer(Mixer):
         aa.window, aa.scale = s.window or 0, self.scale
         aa.sink = None if self.sink is None else self.sink.data_ptr()
         if decode:
-            fast = (ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
-                    and self.sink is None)               # (the tensor-core kernels take no sink: not asked, so not compiled either)
+            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
             chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
@@ -317,7 +316,7 @@ class AttentionMixer(Mixer):
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * qkv.element_size(), width
-            mode = ctx.options.get("attention", "fast") if self.sink is None else "plain"   # "fast" | "mma" | "plain"
+            mode = ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
             # The tensor-core kernels read keys and values from the step's own rows when every sequence starts at
             # position 0, and else from the cache's pages, if the step's keys lie there already (a cache that keeps
             # everything; a reader of another layer's cache finds them there in any case).
@@ -326,6 +325,8 @@ class AttentionMixer(Mixer):
             elif view.ring_rows == 0 and (self.shared or append_now):
                 source = K.KV_FROM_CACHE
             else:
+                source = K.KV_NOWHERE
+            if hd not in (64, 128):                       # the sizes the tensor-core kernels are built for: no other asks for (and compiles) them
                 source = K.KV_NOWHERE
             if mode == "fast" and source and K.attn_prefill_tc_accepts(aa, q_buf.dtype, source):
                 K.attn_prefill_tc(aa, source, ctx.stream)

@@ -134,5 +134,5 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, Tuple[int, ...], t
             if tuple(t.shape) != tuple(shape) or t.dtype != dtype:
                 raise ValueError(f"tensor '{name}' was announced as {dtype} {shape}, produced {t.dtype} {tuple(t.shape)}")
             t = t.detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")      # (reshape: a tensor without dimensions has no bytes view)
     os.replace(tmp, path)

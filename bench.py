@@ -586,6 +586,24 @@ def tefezen_config(width, layers, heads, experts, top, ff, shared_ff, window, vo
             "token_side": {"dim": side}, "layers": out}
 
 
+def zadinex_config(width, layers, heads, experts, top, ff, shared_ff, window=None, vocab=32768):
+    """A Zadinex model of the same sizes: layers alternate attention (heads of 128, a quarter as many kv heads, half of a
+    head rotated, values blended from the second attention layer on) and the wkv recurrence (heads of 64); the first layer
+    has the dense feed-forward (as wide as what a token uses of a mixture), the others mixtures with four pass-through
+    experts, in four groups of which two are open."""
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "identity": 4, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": top * ff + shared_ff} if i == 0 else moe
+        if i % 2 == 0:
+            out.append({"type": "attention", "mlp": mlp,
+                        "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
+                                  "scale": 128 ** -0.5, "v_mix": True}})
+        else:
+            out.append({"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "rank": 64}, "mlp": mlp})
+    return {"architecture": "Zadinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def qwen3_like(width, layers, heads, ffn, vocab=32768):
     """The dense model of equal size: the same width, depth and heads, and a feed-forward as wide as what one token uses
     of the mixture (its chosen experts and the shared one)."""
@@ -600,7 +618,8 @@ def launcher_times(engine, torch, K, entries):
     names = [n for n in ("embed", "scale_f32", "rmsnorm", "rmsnorm_add", "round_rows", "gelu_mul_table", "gemm_simt", "gemm_simt_batched", "gemm_rows",
                          "gemm_tc", "gemm_tc_expert_runs", "gemm_tc_normed", "qk_norm_rope", "kv_append", "attn_prefill", "attn_decode", "attn_decode_mma",
                          "attn_prefill_mma", "attn_prefill_tc", "attn_prefill_split", "moe_gather", "latent_prep", "latent_append", "lightning_scan", "lightning_chunks",
-                         "gated_rmsnorm", "moe_route", "token_gate_rows", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc") if hasattr(K, n)]
+                         "gated_rmsnorm", "moe_route", "token_gate_rows", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc",
+                         "dyt", "scale_add", "wkv", "moe_route_all") if hasattr(K, n)]
     events, originals = [], {n: getattr(K, n) for n in names}
 
     def wrap(name, f):
@@ -609,7 +628,7 @@ def launcher_times(engine, torch, K, entries):
             a0.record()
             r = f(*a, **k)
             a1.record()
-            events.append((name, a0, a1))
+            events.append((name + "_" + ("shift", "decay", "scan", "out")[a[1]] if name == "wkv" else name, a0, a1))
             return r
         return g
     for n, f in originals.items():
@@ -628,8 +647,9 @@ def launcher_times(engine, torch, K, entries):
 
 
 def run_design(args):
-    """``--design tefezen``: prompt and decode throughput of the Tefezen design at sizes that resemble a served model's
-    layers (random weights), beside the Qwen3 dense model of equal size, and where a step's time goes by launcher."""
+    """``--design tefezen | zadinex``: prompt and decode throughput of that design at sizes that resemble a served model's
+    layers (random weights), beside the Qwen3 dense model of equal size (and, for zadinex, beside Tefezen, the closest
+    design: windowed attention, a recurrence, mixtures of experts), and where a step's time goes by launcher."""
     import torch
 
     from titan_b200 import Engine, StepEntry, kernels as K
@@ -643,8 +663,10 @@ def run_design(args):
     results = []
     for sz in sizes:
         row = {"size": sz}
-        for which in ("tefezen", "qwen3"):
-            if which == "tefezen":
+        for which in ((args.design, "qwen3") if args.design == "tefezen" else (args.design, "tefezen", "qwen3")):
+            if which == "zadinex":
+                cfg = zadinex_config(**sz)
+            elif which == "tefezen":
                 cfg = tefezen_config(**sz)
             else:
                 cfg = qwen3_like(sz["width"], sz["layers"], sz["heads"], sz["top"] * sz["ff"] + sz["shared_ff"])
@@ -670,7 +692,7 @@ def run_design(args):
             del engine
             torch.cuda.empty_cache()
         results.append(row)
-    print(json.dumps({"design": "tefezen", "beside": "qwen3 dense of equal width, depth, heads and per-token feed-forward width", "dtype": "bf16",
+    print(json.dumps({"design": args.design, "beside": "qwen3 dense of equal width, depth, heads and per-token feed-forward width", "dtype": "bf16",
                       "data": "synthetic", "prefill_tokens": T, "decode_after_tokens": kv, "peaks": pk, "sizes": results}))
     return 0
 
@@ -693,7 +715,7 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     ap.add_argument("--timeline", type=int, default=0, metavar="BATCH", help="when the CTAs of one captured decode step's kernels start, wait and end "
                     "(needs TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE); text lines, not the JSON line")
-    ap.add_argument("--design", default=None, choices=["tefezen"], help="prompt and decode throughput of another design at a few sizes beside "
+    ap.add_argument("--design", default=None, choices=["tefezen", "zadinex"], help="prompt and decode throughput of another design at a few sizes beside "
                     "the dense model of equal size; one JSON line of its own, the default workload is not run")
     ap.add_argument("--design-size", type=int, default=None, choices=[0, 1], help="with --design: one of its sizes only")
     args = ap.parse_args()

@@ -59,21 +59,47 @@ __global__ void __launch_bounds__(256) wkv_shift_kernel(WkvArgs a) {
     }
 }
 
+// A block takes DEC_TOK tokens and 128 channels: the channels' rows of W2 and the tokens' tanh rows go through shared
+// memory in pieces of DEC_J columns of the rank (W2 rows padded by one against bank conflicts), so W2 is read once per
+// DEC_TOK tokens and every read of it is along its rows.
+#define DEC_TOK 16
+#define DEC_J 64
 template <typename T>
 __global__ void __launch_bounds__(128) wkv_decay_kernel(WkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float th[];           // tanh of the token's low-rank row
-    const int t = blockIdx.x, N = a.H * a.dk;
-    const T* row = (const T*)a.lora + (size_t)t * a.lora_stride;
-    for (int j = threadIdx.x; j < a.rank; j += blockDim.x) th[j] = tanhf(ldf(row + j));
-    __syncthreads();
-    const int n = blockIdx.y * 128 + threadIdx.x;
+    __shared__ float w2s[128][DEC_J + 1];
+    __shared__ float ths[DEC_TOK][DEC_J];
+    const int N = a.H * a.dk, tid = threadIdx.x;
+    const int t0 = blockIdx.x * DEC_TOK, n0 = blockIdx.y * 128, n = n0 + tid;
+    const int n_tok = min(DEC_TOK, a.T - t0);
+    float acc[DEC_TOK];
+#pragma unroll
+    for (int t = 0; t < DEC_TOK; ++t) acc[t] = 0.f;
+    for (int j0 = 0; j0 < a.rank; j0 += DEC_J) {
+        const int nj = min(DEC_J, a.rank - j0);
+        __syncthreads();
+        for (int e = tid; e < 128 * DEC_J; e += 128) {
+            const int r = e / DEC_J, j = e % DEC_J;
+            w2s[r][j] = (n0 + r < N && j < nj) ? ldf((const T*)a.w2 + (size_t)(n0 + r) * a.rank + j0 + j) : 0.f;
+        }
+        for (int e = tid; e < DEC_TOK * DEC_J; e += 128) {
+            const int t = e / DEC_J, j = e % DEC_J;
+            ths[t][j] = (t < n_tok && j < nj) ? tanhf(ldf((const T*)a.lora + (size_t)(t0 + t) * a.lora_stride + j0 + j)) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int j = 0; j < DEC_J; ++j) {
+            const float wv = w2s[tid][j];
+#pragma unroll
+            for (int t = 0; t < DEC_TOK; ++t) acc[t] = fmaf(wv, ths[t][j], acc[t]);
+        }
+    }
     if (n >= N) return;
-    const T* w = (const T*)a.w2 + (size_t)n * a.rank;
-    float z = 0.f;
-    for (int j = 0; j < a.rank; ++j) z = fmaf(ldf(w + j), th[j], z);
-    a.decay[(size_t)t * N + n] = expf(-expf(z + a.w0[n]));
+    const float w0 = a.w0[n];
+#pragma unroll
+    for (int t = 0; t < DEC_TOK; ++t)
+        if (t < n_tok) a.decay[(size_t)(t0 + t) * N + n] = expf(-expf(acc[t] + w0));
 }
 
 template <typename T, int R, int CH>
@@ -83,7 +109,6 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
     extern __shared__ __align__(16) float sm[];
     constexpr int DKP = 4 * (R + 4);                    // a row of dk numbers in shared memory: four runs of R, each padded by 4
     constexpr int ROW = 4 * DKP + 32;                   // r | k | w | r * u | 32 values
-    constexpr int PER = (CH * (12 * R + 32) + 127) / 128;
     const int b = blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, s = tid & 3, col = tid >> 2, j = blockIdx.z * 32 + col;
     const int dk = a.dk, N = a.H * dk;
@@ -99,59 +124,57 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
     }
     const T* proj = (const T*)a.proj;
     const float* bonus = a.u + (size_t)h * dk;
-    const int per_tok = 3 * dk + 32, total = CH * per_tok;
-    // Element e of a chunk: token e / per_tok, then r, k, w (dk each) and the block's 32 values.  ``fetch`` reads it from a
-    // valid address in every case (indices are clamped, so the load carries no condition); ``place`` says where it goes in
-    // shared memory, whether it is real, and which key channel it belongs to (r only: its product with the bonus goes
-    // DKP * 3 further on).
-    auto fetch = [&](int u, int first) -> float {
-        const int e = min(tid + 128 * u, total - 1), tok = e / per_tok, x = e % per_tok;
-        const size_t row = (size_t)min(first + tok, t1 - 1);
-        if (x < 3 * dk) {
-            const int arr = x / dk, i = x - arr * dk;
-            if (arr == 2) return a.decay[row * N + h * dk + i];
-            return ldf(proj + row * a.proj_stride + (size_t)arr * N + h * dk + i);
-        }
-        const int c = min(blockIdx.z * 32 + (x - 3 * dk), dk - 1);
-        return ldf(proj + row * a.proj_stride + (size_t)2 * N + h * dk + c);
-    };
-    auto place = [&](int u, int first, int* to, int* channel) -> bool {
-        const int e = tid + 128 * u, ec = min(e, total - 1), tok = ec / per_tok, x = ec % per_tok;
-        bool ok = e < total && first + tok < t1;
-        *channel = -1;
-        if (x < 3 * dk) {
-            const int arr = x / dk, i = x - arr * dk;
-            *to = tok * ROW + arr * DKP + (i / R) * (R + 4) + (i % R);
-            if (arr == 0) *channel = i;
-            return ok;
-        }
-        const int c = x - 3 * dk;
-        *to = tok * ROW + 4 * DKP + c;
-        return ok && blockIdx.z * 32 + c < dk;
-    };
-    float stage[PER];
-    for (int e = tid; e < CH * ROW; e += 128) sm[e] = 0.f;       // the padding between runs and rows beyond dk are factors: zero
-    if (t0 < t1) {
+    // Staging.  A token's row of the chunk has 3 dk + 32 elements: r, k, w (dk each) and the block's 32 values.  A thread
+    // takes columns tid, tid + 128, ... of every token of the chunk; what a column is (which array, where it comes from,
+    // where it goes in shared memory, its bonus) is worked out once, before the first chunk, so that the loop over chunks
+    // divides nothing.  Loads are from valid addresses in every case (rows are clamped), so they carry no condition.
+    constexpr int XI = (12 * R + 32 + 127) / 128;
+    const int per_tok = 3 * dk + 32;
+    int src[XI], to[XI];            // column in the source row (r, k, v: of proj; w: of decay); offset in a token's shared row; to < 0: no such column
+    bool from_decay[XI];
+    float bonus_of[XI];             // r only: the bonus of its channel (its product goes 3 DKP further on); else 0 and unused
+    bool is_r[XI];
 #pragma unroll
-        for (int u = 0; u < PER; ++u) stage[u] = fetch(u, t0);
+    for (int xi = 0; xi < XI; ++xi) {
+        const int x = tid + 128 * xi;
+        src[xi] = 0; to[xi] = -1; from_decay[xi] = false; bonus_of[xi] = 0.f; is_r[xi] = false;
+        if (x < 3 * dk) {
+            const int arr = x / dk, i = x - arr * dk;
+            to[xi] = arr * DKP + (i / R) * (R + 4) + (i % R);
+            from_decay[xi] = arr == 2;
+            src[xi] = arr == 2 ? h * dk + i : arr * N + h * dk + i;
+            if (arr == 0) { is_r[xi] = true; bonus_of[xi] = bonus[i]; }
+        } else if (x < per_tok) {
+            const int c = x - 3 * dk;
+            if (blockIdx.z * 32 + c < dk) { to[xi] = 4 * DKP + c; src[xi] = 2 * N + h * dk + blockIdx.z * 32 + c; }
+        }
     }
+    float stage[XI][CH];
+    auto fetch = [&](int first) {
+#pragma unroll
+        for (int xi = 0; xi < XI; ++xi)
+#pragma unroll
+            for (int tok = 0; tok < CH; ++tok) {
+                const size_t row = (size_t)min(first + tok, t1 - 1);
+                stage[xi][tok] = from_decay[xi] ? a.decay[row * N + src[xi]] : ldf(proj + row * a.proj_stride + src[xi]);
+            }
+    };
+    for (int e = tid; e < CH * ROW; e += 128) sm[e] = 0.f;       // the padding between runs and rows beyond dk are factors: zero
+    if (t0 < t1) fetch(t0);
     for (int c0 = t0; c0 < t1; c0 += CH) {
         __syncthreads();                                // the chunk before has been read (or the zeros are in place)
 #pragma unroll
-        for (int u = 0; u < PER; ++u) {
-            if (tid + 128 * u < total) {
-                int to, channel;
-                const bool real = place(u, c0, &to, &channel);
-                const float v = real ? stage[u] : 0.f;
-                sm[to] = v;
-                if (channel >= 0) sm[to + 3 * DKP] = v * bonus[channel];
+        for (int xi = 0; xi < XI; ++xi) {
+            if (to[xi] < 0) continue;
+#pragma unroll
+            for (int tok = 0; tok < CH; ++tok) {
+                const float v = c0 + tok < t1 ? stage[xi][tok] : 0.f;
+                sm[tok * ROW + to[xi]] = v;
+                if (is_r[xi]) sm[tok * ROW + to[xi] + 3 * DKP] = v * bonus_of[xi];
             }
         }
         __syncthreads();
-        if (c0 + CH < t1) {
-#pragma unroll
-            for (int u = 0; u < PER; ++u) stage[u] = fetch(u, c0 + CH);
-        }
+        if (c0 + CH < t1) fetch(c0 + CH);
         const int n = min(CH, t1 - c0);
         for (int tt = 0; tt < n; ++tt) {
             const float* rs = sm + tt * ROW + s * (R + 4);
@@ -159,17 +182,17 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
             const float* ws = ks + DKP;
             const float* us = ws + DKP;
             const float vj = sm[tt * ROW + 4 * DKP + col];
-            float acc = 0.f, now = 0.f;
+            float acc = 0.f, acc2 = 0.f, now = 0.f, now2 = 0.f;      // two chains each, so that a sum does not wait for the one before it
 #pragma unroll
             for (int ii = 0; ii < R; ii += 4) {
                 const float4 r4 = *reinterpret_cast<const float4*>(rs + ii), k4 = *reinterpret_cast<const float4*>(ks + ii);
                 const float4 w4 = *reinterpret_cast<const float4*>(ws + ii), u4 = *reinterpret_cast<const float4*>(us + ii);
-                acc = fmaf(S[ii], r4.x, acc);     now = fmaf(u4.x, k4.x, now); S[ii] = fmaf(w4.x, S[ii], k4.x * vj);
-                acc = fmaf(S[ii + 1], r4.y, acc); now = fmaf(u4.y, k4.y, now); S[ii + 1] = fmaf(w4.y, S[ii + 1], k4.y * vj);
-                acc = fmaf(S[ii + 2], r4.z, acc); now = fmaf(u4.z, k4.z, now); S[ii + 2] = fmaf(w4.z, S[ii + 2], k4.z * vj);
-                acc = fmaf(S[ii + 3], r4.w, acc); now = fmaf(u4.w, k4.w, now); S[ii + 3] = fmaf(w4.w, S[ii + 3], k4.w * vj);
+                acc = fmaf(S[ii], r4.x, acc);      now = fmaf(u4.x, k4.x, now);   S[ii] = fmaf(w4.x, S[ii], k4.x * vj);
+                acc2 = fmaf(S[ii + 1], r4.y, acc2); now2 = fmaf(u4.y, k4.y, now2); S[ii + 1] = fmaf(w4.y, S[ii + 1], k4.y * vj);
+                acc = fmaf(S[ii + 2], r4.z, acc);  now = fmaf(u4.z, k4.z, now);   S[ii + 2] = fmaf(w4.z, S[ii + 2], k4.z * vj);
+                acc2 = fmaf(S[ii + 3], r4.w, acc2); now2 = fmaf(u4.w, k4.w, now2); S[ii + 3] = fmaf(w4.w, S[ii + 3], k4.w * vj);
             }
-            acc = fmaf(now, vj, acc);                   // the current token's own pair, weighted by the bonus
+            acc = fmaf(now + now2, vj, acc + acc2);     // the current token's own pair, weighted by the bonus
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + h * dk + j] = acc;
@@ -224,11 +247,11 @@ cudaError_t launch_scan(const WkvArgs& a, cudaStream_t stream) {
 template <typename T>
 int run(const WkvArgs& a, int stage, cudaStream_t stream) {
     if (stage == 0) tb_launch(wkv_shift_kernel<T>, a.T, 256, 0, stream, a);
-    else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3(a.T, (a.H * a.dk + 127) / 128), 128, (size_t)a.rank * sizeof(float), stream, a);
+    else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3((a.T + DEC_TOK - 1) / DEC_TOK, (a.H * a.dk + 127) / 128), 128, 0, stream, a);
     else if (stage == 2) {
         if (a.dk <= 32) launch_scan<T, 8, 16>(a, stream);
         else if (a.dk <= 64) launch_scan<T, 16, 16>(a, stream);
-        else if (a.dk <= 128) launch_scan<T, 32, 16>(a, stream);
+        else if (a.dk <= 128) launch_scan<T, 32, 8>(a, stream);
         else launch_scan<T, 64, 8>(a, stream);
     } else tb_launch(wkv_out_kernel<T>, dim3(a.T, (a.H + 3) / 4), 128, 0, stream, a);
     return 0;

@@ -99,3 +99,17 @@ def test_the_plain_router_keeps_to_open_groups_and_counts_negative_scores():
     idx, w = P.routed_choice(h, f, W, "r.")
     assert all(int(a) // 2 == int(b) // 2 for a, b in idx.tolist())         # both from one group
     assert torch.allclose(w.sum(-1), torch.ones(3, dtype=torch.float64))
+
+
+def test_a_folder_of_random_weights_is_written_and_read_back(tmp_path):
+    """The random-weights mode on this design: tensors without dimensions (a norm's factor, a blending factor) included."""
+    from titan_b200.config import config_from_dict, load_config
+    from titan_b200.parts import declare_weights
+    from titan_b200.weights import FolderWeights, write_model_folder
+    folder = write_model_folder(str(tmp_path / "m"), config_from_dict(make_config("odd")), seed=4)
+    cfg = load_config(folder)
+    declared = declare_weights(cfg.to_model_spec())
+    source = FolderWeights(folder, declared, torch.float32, "cpu")
+    by_name = {w.name: w for w in declared}
+    assert source.get(by_name["l2.mix.vmix"]).shape == () and source.get(by_name["final.norm.alpha"]).dtype == torch.float32
+    assert source.get(by_name["l0.mix.w2"]).shape == (40, 3)

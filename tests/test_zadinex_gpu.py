@@ -229,7 +229,8 @@ def test_one_far_key_decides(dtype, dim, far):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,dk,rank", [(3, 8, 5), (1, 40, 3), (2, 64, 16), (2, 20, 9), (1, 130, 7), (4, 32, 32)])
+@pytest.mark.parametrize("H,dk,rank", [(3, 8, 5), (1, 40, 3), (2, 64, 16), (2, 20, 9), (1, 130, 7), (4, 32, 32),
+                                          (80, 8, 4), (40, 64, 6), (20, 128, 5)])      # the last three: heads enough for the kernel of four lanes a column
 def test_wkv_alone(dtype, H, dk, rank):
     """Two sequences through whole prompts, portions of two tokens and single tokens, then the slots given back and used
     again: outputs, and a state that starts from zero for the next owner."""
@@ -570,3 +571,14 @@ def test_trace_runner_as_a_subprocess(tmp_path):
     rows_close(one, torch.stack([pa[60], pb[20]]), "float32", "step 1")
     last = torch.from_numpy(np.fromfile(out / "10.f32", dtype="<f4").reshape(-1, V))
     rows_close(last, pa[69:70], "float32", "step 10")
+
+
+def test_command_line_with_random_weights(tmp_path):
+    """bin/titan_b200 run --random: the design through the command line, the scheduler and the sampler, from a description alone."""
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(make_config("mix")))
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "titan_b200"), "run", "--random", str(path), "--weights-seed", "3", "--prompt-ids", "5,6,7,8",
+                        "--prompt-ids", "9,10", "--max-tokens", "12", "--temp", "0", "--dtype", "bfloat16", "--kv-capacity", "512"],
+                       capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.strip(), "nothing was generated"

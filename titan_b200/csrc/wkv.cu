@@ -12,9 +12,9 @@
 //
 //   tb_wkv_shift   the five mixes of every token, side by side in one row (a block a token)
 //   tb_wkv_decay   w of every token and channel from the low-rank product's first half (tanh, the second product, w0, exp(-exp))
-//   tb_wkv_scan    the recurrence; grid (sequences, heads, ceil(dk / 32)): a block owns 32 value columns of one head's state,
-//                  four neighbouring lanes share a column (a quarter of its rows each, in registers) and add their parts of
-//                  o by two shuffles; tokens are staged in shared memory a chunk at a time, the next chunk's loads in
+//   tb_wkv_scan    the recurrence; grid (sequences, heads, ceil(dk / 32 or 16)): a block owns 32 (or 16) value columns of one
+//                  head's state, four (or eight) neighbouring lanes share a column (a share of its rows each, in registers)
+//                  and add their parts of o by shuffles; tokens are staged in shared memory a chunk at a time, the next chunk's loads in
 //                  flight while this one is worked through.  Tokens are taken in order whatever the step brings, so a
 //                  prompt run whole, in pieces or token by token leaves the same state.  The block of head 0 also
 //                  leaves the sequence's last input row in the state.
@@ -102,15 +102,19 @@ __global__ void __launch_bounds__(128) wkv_decay_kernel(WkvArgs a) {
         if (t < n_tok) a.decay[(size_t)(t0 + t) * N + n] = expf(-expf(acc[t] + w0));
 }
 
-template <typename T, int R, int CH>
+// LPC lanes share a column of the state (R rows of it each: dk <= LPC * R), so a block of 128 threads owns COLS = 128 / LPC
+// value columns.  Four lanes a column where the launch has blocks enough to fill the machine; eight (half the rows a thread,
+// twice the blocks) where it has not: a token's chain of dependent sums is then half as long.
+template <typename T, int R, int CH, int LPC>
 __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int DKP = 4 * (R + 4);                    // a row of dk numbers in shared memory: four runs of R, each padded by 4
-    constexpr int ROW = 4 * DKP + 32;                   // r | k | w | r * u | 32 values
+    constexpr int COLS = 128 / LPC;
+    constexpr int DKP = LPC * (R + 4);                  // a row of dk numbers in shared memory: LPC runs of R, each padded by 4
+    constexpr int ROW = 4 * DKP + COLS;                 // r | k | w | r * u | the block's values
     const int b = blockIdx.x, h = blockIdx.y;
-    const int tid = threadIdx.x, s = tid & 3, col = tid >> 2, j = blockIdx.z * 32 + col;
+    const int tid = threadIdx.x, s = tid % LPC, col = tid / LPC, j = blockIdx.z * COLS + col;
     const int dk = a.dk, N = a.H * dk;
     const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
     const bool live = j < dk;
@@ -124,12 +128,12 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
     }
     const T* proj = (const T*)a.proj;
     const float* bonus = a.u + (size_t)h * dk;
-    // Staging.  A token's row of the chunk has 3 dk + 32 elements: r, k, w (dk each) and the block's 32 values.  A thread
+    // Staging.  A token's row of the chunk has 3 dk + COLS elements: r, k, w (dk each) and the block's values.  A thread
     // takes columns tid, tid + 128, ... of every token of the chunk; what a column is (which array, where it comes from,
     // where it goes in shared memory, its bonus) is worked out once, before the first chunk, so that the loop over chunks
     // divides nothing.  Loads are from valid addresses in every case (rows are clamped), so they carry no condition.
-    constexpr int XI = (12 * R + 32 + 127) / 128;
-    const int per_tok = 3 * dk + 32;
+    constexpr int XI = (3 * LPC * R + COLS + 127) / 128;
+    const int per_tok = 3 * dk + COLS;
     int src[XI], to[XI];            // column in the source row (r, k, v: of proj; w: of decay); offset in a token's shared row; to < 0: no such column
     bool from_decay[XI];
     float bonus_of[XI];             // r only: the bonus of its channel (its product goes 3 DKP further on); else 0 and unused
@@ -146,7 +150,7 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
             if (arr == 0) { is_r[xi] = true; bonus_of[xi] = bonus[i]; }
         } else if (x < per_tok) {
             const int c = x - 3 * dk;
-            if (blockIdx.z * 32 + c < dk) { to[xi] = 4 * DKP + c; src[xi] = 2 * N + h * dk + blockIdx.z * 32 + c; }
+            if (blockIdx.z * COLS + c < dk) { to[xi] = 4 * DKP + c; src[xi] = 2 * N + h * dk + blockIdx.z * COLS + c; }
         }
     }
     float stage[XI][CH];
@@ -176,6 +180,10 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
         __syncthreads();
         if (c0 + CH < t1) fetch(c0 + CH);
         const int n = min(CH, t1 - c0);
+        // (a block is one warp a scheduler: unrolled, the loads, sums and shuffles of neighbouring tokens overlap; only the
+        // state's own update runs from token to token)
+        constexpr int TOGETHER = R >= 32 ? 1 : 4;        // (wide heads hold too many rows a thread to hold several tokens as well)
+#pragma unroll TOGETHER
         for (int tt = 0; tt < n; ++tt) {
             const float* rs = sm + tt * ROW + s * (R + 4);
             const float* ks = rs + DKP;
@@ -193,8 +201,8 @@ __global__ void __launch_bounds__(128) wkv_scan_kernel(WkvArgs a) {
                 acc2 = fmaf(S[ii + 3], r4.w, acc2); now2 = fmaf(u4.w, k4.w, now2); S[ii + 3] = fmaf(w4.w, S[ii + 3], k4.w * vj);
             }
             acc = fmaf(now + now2, vj, acc + acc2);     // the current token's own pair, weighted by the bonus
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+#pragma unroll
+            for (int o = 1; o < LPC; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + h * dk + j] = acc;
         }
     }
@@ -233,15 +241,16 @@ __global__ void __launch_bounds__(128) wkv_out_kernel(WkvArgs a) {
     }
 }
 
-template <typename T, int R, int CH>
+template <typename T, int R, int CH, int LPC>
 cudaError_t launch_scan(const WkvArgs& a, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)CH * (4 * 4 * (R + 4) + 32) * sizeof(float);
+    constexpr int COLS = 128 / LPC;
+    constexpr size_t smem = (size_t)CH * (4 * LPC * (R + 4) + COLS) * sizeof(float);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        cudaFuncSetAttribute(wkv_scan_kernel<T, R, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(wkv_scan_kernel<T, R, CH, LPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         raised = true;
     }
-    return tb_launch(wkv_scan_kernel<T, R, CH>, dim3(a.B, a.H, (a.dk + 31) / 32), 128, smem, stream, a);
+    return tb_launch(wkv_scan_kernel<T, R, CH, LPC>, dim3(a.B, a.H, (a.dk + COLS - 1) / COLS), 128, smem, stream, a);
 }
 
 template <typename T>
@@ -249,10 +258,16 @@ int run(const WkvArgs& a, int stage, cudaStream_t stream) {
     if (stage == 0) tb_launch(wkv_shift_kernel<T>, a.T, 256, 0, stream, a);
     else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3((a.T + DEC_TOK - 1) / DEC_TOK, (a.H * a.dk + 127) / 128), 128, 0, stream, a);
     else if (stage == 2) {
-        if (a.dk <= 32) launch_scan<T, 8, 16>(a, stream);
-        else if (a.dk <= 64) launch_scan<T, 16, 16>(a, stream);
-        else if (a.dk <= 128) launch_scan<T, 32, 8>(a, stream);
-        else launch_scan<T, 64, 8>(a, stream);
+        // eight lanes a column while four would leave SMs without a block (148 on this chip), for heads up to 128 wide
+        const bool few = (long long)a.B * a.H * ((a.dk + 31) / 32) < 148 && a.dk <= 128;
+        if (few) {
+            if (a.dk <= 32) launch_scan<T, 4, 16, 8>(a, stream);
+            else if (a.dk <= 64) launch_scan<T, 8, 16, 8>(a, stream);
+            else launch_scan<T, 16, 16, 8>(a, stream);
+        } else if (a.dk <= 32) launch_scan<T, 8, 16, 4>(a, stream);
+        else if (a.dk <= 64) launch_scan<T, 16, 16, 4>(a, stream);
+        else if (a.dk <= 128) launch_scan<T, 32, 8, 4>(a, stream);
+        else launch_scan<T, 64, 8, 4>(a, stream);
     } else tb_launch(wkv_out_kernel<T>, dim3(a.T, (a.H + 3) / 4), 128, 0, stream, a);
     return 0;
 }

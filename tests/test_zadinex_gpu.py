@@ -143,7 +143,7 @@ ATTENTION_SIZES = [
     (4, 2, 16, 16, 8, 300.0),          # a part of the head rotated
     (3, 1, 12, 20, 4, 50.0),           # keys and values of unequal widths, no multiples of 8: padded in the cache
     (6, 6, 24, 8, 24, 1e4),            # as many kv heads as heads; the whole head rotated; values narrower than keys
-    (4, 2, 64, 64, 32, 5e4),           # bfloat16: the mma.sync kernels
+    (4, 2, 64, 64, 48, 3e4),           # bfloat16: the mma.sync kernels
     (2, 1, 128, 128, 64, 1e4),         # bfloat16: the tcgen05 prompt kernel
 ]
 
@@ -308,7 +308,7 @@ def test_router_choice_and_weights(E, top, identity, groups, keep):
     (6, 2, 24, 1.5, 2, 4, 2, 7),        # a few pairs: a warp per output
     (5, 1, 18, 0.7, 0, 1, 1, 150),      # one expert a token; a limit that clamps often
     (3, 2, 10, 2.5, 3, 3, 1, 90),       # as many pass-through experts as real ones
-    (8, 2, 64, 1.0, 2, 2, 1, 700),      # bfloat16: rows gathered by expert, tensor-core products
+    (10, 2, 72, 1.0, 2, 3, 1, 700),     # bfloat16: rows gathered by expert, tensor-core products
 ])
 def test_mixture_of_experts_alone(dtype, E, top, F, limit, identity, groups, keep, T):
     from titan_b200.parts import FEED_FORWARDS

@@ -47,9 +47,9 @@ CASES = {
                          width=56, vocab=131, eps=3e-6),
     # heads of 64 and of 128: in bfloat16 the tensor-core attention kernels and the tensor-core products; a first attention
     # layer that does not blend, then two that do
-    "wide": lambda: model([with_mlp(attention(4, 2, 64, 64, 32, base=50000.0, scale=0.125), dense(192)),
-                           with_mlp(attention(4, 2, 64, 64, 32, base=50000.0, scale=0.125, v_mix=True), moe(8, 2, 64, 1.5, identity=2, groups=(2, 1))),
-                           with_mlp(wkv(4, 64, 16), moe(8, 3, 64, 1.0, groups=(4, 3))),
+    "wide": lambda: model([with_mlp(attention(4, 2, 64, 64, 16, base=30000.0, scale=0.14), dense(192)),
+                           with_mlp(attention(4, 2, 64, 64, 16, base=30000.0, scale=0.14, v_mix=True), moe(10, 2, 80, 1.25, identity=2, groups=(3, 1))),
+                           with_mlp(wkv(4, 64, 24), moe(8, 3, 64, 1.0, groups=(4, 3))),
                            with_mlp(attention(2, 2, 64, 64, 64, scale=0.11, v_mix=True), dense(128)),
                            with_mlp(attention(2, 1, 128, 128, 64, scale=0.09), dense(128))],
                           width=128, vocab=211, eps=1e-6),

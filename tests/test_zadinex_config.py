@@ -38,8 +38,11 @@ def test_declared_tensors_are_the_plain_list(name):
     from titan_b200.config import config_from_dict
     from titan_b200.parts import declare_weights
     cfg = make_config(name)
-    declared = {w.name: tuple(w.shape) for w in declare_weights(config_from_dict(cfg).to_model_spec())}
-    assert declared == {n: tuple(s) for n, s, _ in P.tensor_list(cfg)}
+    spec = config_from_dict(cfg).to_model_spec()
+    declared = {w.name: tuple(w.shape) for w in declare_weights(spec)}
+    plain = {n: tuple(s) for n, s, _ in P.tensor_list(cfg)}
+    assert all(plain[n] == s for n, s in declared.items())
+    assert set(plain) - set(declared) <= set(spec.ignorable_tensors)       # the first blending layer's factor: in the file, used by nobody
 
 
 def test_rank_comes_from_the_tensor_where_the_description_has_none(tmp_path):
@@ -111,5 +114,23 @@ def test_a_folder_of_random_weights_is_written_and_read_back(tmp_path):
     declared = declare_weights(cfg.to_model_spec())
     source = FolderWeights(folder, declared, torch.float32, "cpu")
     by_name = {w.name: w for w in declared}
-    assert source.get(by_name["l2.mix.vmix"]).shape == () and source.get(by_name["final.norm.alpha"]).dtype == torch.float32
+    assert "l2.mix.vmix" not in by_name                      # the only blending layer: nobody uses its factor, so it is not written
+    assert source.get(by_name["l0.norm1.alpha"]).shape == () and source.get(by_name["final.norm.alpha"]).dtype == torch.float32
     assert source.get(by_name["l0.mix.w2"]).shape == (40, 3)
+
+
+def test_factors_of_switched_off_mechanisms_may_be_in_the_file(tmp_path):
+    """A layer that does not blend values may still carry its factor, a layer without feed-forward its second norm and scale."""
+    from titan_b200.config import load_config
+    from titan_b200.parts import declare_weights
+    from titan_b200.weights import FolderWeights, WeightError
+    cfg = make_config("odd")
+    weights = {k: v.to(torch.bfloat16) for k, v in P.random_weights(cfg, 2).items()}
+    weights["l1.mix.vmix"] = torch.tensor(0.5, dtype=torch.bfloat16)
+    weights["l1.ls2"] = torch.ones(cfg["width"], dtype=torch.bfloat16)
+    folder = write_folder(str(tmp_path / "m"), cfg, weights)
+    spec = load_config(folder).to_model_spec()
+    assert "l1.mix.vmix" in spec.ignorable_tensors and "l1.ls2" in spec.ignorable_tensors and "l0.ls2" not in spec.ignorable_tensors
+    FolderWeights(folder, declare_weights(spec), torch.float32, "cpu", spec.ignorable_tensors)
+    with pytest.raises(WeightError):
+        FolderWeights(folder, declare_weights(spec), torch.float32, "cpu")

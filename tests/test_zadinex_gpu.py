@@ -229,7 +229,7 @@ def test_one_far_key_decides(dtype, dim, far):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,dk,rank", [(3, 8, 5), (1, 40, 3), (2, 64, 16), (2, 20, 9), (1, 130, 7), (4, 32, 32),
+@pytest.mark.parametrize("H,dk,rank", [(3, 8, 5), (1, 40, 3), (2, 64, 16), (2, 20, 9), (1, 130, 7), (4, 32, 32), (2, 96, 8),
                                           (80, 8, 4), (40, 64, 6), (20, 128, 5)])      # the last three: heads enough for the kernel of four lanes a column
 def test_wkv_alone(dtype, H, dk, rank):
     """Two sequences through whole prompts, portions of two tokens and single tokens, then the slots given back and used

@@ -127,6 +127,9 @@ class ModelSpec:
     # Tensors that no single layer owns (a table that every layer reads a slice of): (name, shape) pairs.  The model
     # loads each once and hands the dict to every part that has ``bind_shared``.
     shared_tensors: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+    # Tensors that a file of this model may hold although the model, as described, uses none of them (the factor of a
+    # mechanism that a layer's description switches off): present or absent, they are not an error and are not loaded.
+    ignorable_tensors: Tuple[str, ...] = ()
 
     def validate(self) -> None:
         if not self.layers:

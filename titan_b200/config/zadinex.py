@@ -108,9 +108,13 @@ class ZadinexConfig:
         W, V, eps = d["width"], d["vocab"], float(d["norm"]["eps"])
         norm = lambda name: NormSpec("dyt", W, eps, name)
         first_mixing = next((i for i, l in enumerate(d["layers"]) if l["type"] == "attention" and l["mixer"].get("v_mix")), None)
-        layers = []
+        layers, unused = [], []
         for i, layer in enumerate(d["layers"]):
             m = layer["mixer"]
+            if layer["type"] == "attention" and (not m.get("v_mix") or i == first_mixing):
+                unused.append(f"l{i}.mix.vmix")                # a file may carry the factor of a layer that does not blend, or that the others blend with
+            if layer.get("mlp") is None:
+                unused += [f"l{i}.norm2", f"l{i}.norm2.b", f"l{i}.norm2.alpha", f"l{i}.ls2"]
             if layer["type"] == "attention":
                 extra = [("value_dim", m["vdim"]), ("unit_norm", "after_rotation"), ("unit_norm_eps", eps), ("sink", "sink"), ("layer_index", i)]
                 if m.get("v_mix"):
@@ -139,6 +143,7 @@ class ZadinexConfig:
                                     feed_forward_norm=None if ffn is None else norm("norm2"), prefix=f"l{i}.",
                                     extra=(("scales", ("ls1",) if ffn is None else ("ls1", "ls2")),)))
         spec = ModelSpec(architecture=self.architecture, hidden_size=W, vocab_size=V, layers=tuple(layers), order=tuple(range(len(layers))),
-                         final_norm=norm("final.norm"), embedding="embed", lm_head="head", max_positions=MAX_POSITIONS)
+                         final_norm=norm("final.norm"), embedding="embed", lm_head="head", max_positions=MAX_POSITIONS,
+                         ignorable_tensors=tuple(unused))
         spec.validate()
         return spec

@@ -102,7 +102,8 @@ class Engine:
     @classmethod
     def from_pretrained(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
         config = load_config(model_dir)
-        ignorable = ["lm_head.weight"] if config.to_model_spec().lm_head is None else []
+        spec = config.to_model_spec()
+        ignorable = (["lm_head.weight"] if spec.lm_head is None else []) + list(spec.ignorable_tensors)
         return cls(config, lambda declared, dt, dev: FolderWeights(model_dir, declared, dt, dev, ignorable),
                    EngineOptions(dtype=dtype, **kw))
 
@@ -114,7 +115,8 @@ class Engine:
 
     @classmethod
     def from_tensors(cls, config, tensors: Dict[str, torch.Tensor], dtype="bfloat16", **kw) -> "Engine":
-        return cls(config, lambda declared, dt, dev: DictWeights(tensors, declared, dt, dev), EngineOptions(dtype=dtype, **kw))
+        ignorable = config.to_model_spec().ignorable_tensors
+        return cls(config, lambda declared, dt, dev: DictWeights(tensors, declared, dt, dev, ignorable), EngineOptions(dtype=dtype, **kw))
 
     # -- properties the generation loop reads -------------------------------- #
     @property

@@ -149,7 +149,7 @@ class AttentionMixer(Mixer):
                           WeightSpec(p + n["v"], (s.num_kv_heads * vd, s.hidden_size))]
         if self.sink_name:
             specs.append(WeightSpec(p + self.sink_name, (s.num_heads,), "vector", ("normal", 1.0)))
-        if self.value_mix is not None:
+        if self.value_mix is not None and self.value_mix[0] is not None:      # (the layer the others blend with has no use for a factor)
             specs.append(WeightSpec(p + self.value_mix[1], (), "vector", ("normal", 0.3)))
         if s.qk_norm is not None:
             for which in ("q",) if self.shared else ("q", "k"):
@@ -172,7 +172,7 @@ class AttentionMixer(Mixer):
             self.w_o = torch.nn.functional.pad(w, (0, self.hd - self.value_dim)).reshape(s.hidden_size, self.Q).contiguous()
         if self.sink_name:
             self.sink = get(p + self.sink_name)
-        if self.value_mix is not None:
+        if self.value_mix is not None and self.value_mix[0] is not None:
             self.mix_factor = get(p + self.value_mix[1]).reshape(1)
         if s.qk_norm is not None:
             self.q_norm = get(p + s.qk_norm.weight.format("q"))

@@ -582,3 +582,67 @@ def test_command_line_with_random_weights(tmp_path):
                        capture_output=True, text=True, timeout=900)
     assert p.returncode == 0, p.stderr[-2000:]
     assert p.stdout.strip(), "nothing was generated"
+
+
+def drawn_config(seed):
+    """A configuration drawn at random: sizes, head counts, layer order, options and constants, odd sizes included."""
+    import random
+    from zadinex_cases import attention, dense, model, moe, wkv
+    r = random.Random(seed)
+    width = r.choice([24, 40, 56, 72, 100, 136])
+    blend = None                                              # (kv heads, value width) that blending layers share
+    layers = []
+    for i in range(r.randint(2, 5)):
+        if r.random() < 0.6:
+            kv = r.choice([1, 2, 3])
+            heads = kv * r.choice([1, 2, 4])
+            dim = r.choice([6, 8, 12, 16, 20, 32, 40, 64])
+            vdim = r.choice([dim, dim, 8, 24, 16])
+            v_mix = r.random() < 0.6
+            if v_mix:
+                if blend is None:
+                    blend = (kv, vdim)
+                kv, vdim = blend
+                heads = kv * r.choice([1, 2, 4])
+            rot = r.choice([d for d in (2, 4, 6, 8, 16, 32, 64) if d <= dim])
+            mixer = attention(heads, kv, dim, vdim, rot, base=r.choice([100.0, 1e4, 5e5]), scale=r.choice([0.1, 0.3, dim ** -0.5]), v_mix=v_mix)
+        else:
+            mixer = wkv(r.choice([1, 2, 3, 5]), r.choice([4, 8, 12, 24, 48, 72]), r.choice([1, 4, 7, 16]))
+        kind = r.choice(["dense", "moe", "moe", "none"])
+        if kind == "dense":
+            mlp = dense(r.choice([16, 33, 64, 100]))
+        elif kind == "moe":
+            groups = r.choice([1, 2, 3, 4])
+            per = r.choice([1, 2, 3])
+            n_all = groups * per
+            identity = r.randint(0, n_all - 1)
+            keep = r.randint(1, groups)
+            mlp = moe(n_all - identity, r.randint(1, keep * per), r.choice([8, 12, 32]), r.choice([0.5, 1.5, 4.0]), identity=identity,
+                      groups=(groups, keep) if r.random() < 0.8 or groups > 1 else None)
+        else:
+            mlp = None
+        layers.append(dict(mixer, mlp=mlp))
+    return model(layers, width=width, vocab=r.choice([50, 97, 300]), eps=r.choice([1e-6, 1e-5, 1e-4]))
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("seed", range(int(os.environ.get("ZADINEX_DRAWN", "12"))))
+def test_configurations_drawn_at_random(seed, dtype):
+    """A prompt whole, then a second request as a prompt with single tokens after it, in a batch with a third."""
+    from titan_b200 import Engine, StepEntry
+    from titan_b200.config import config_from_dict
+    cfg = drawn_config(seed)
+    w = P.random_weights(cfg, 100 + seed)
+    e = Engine.from_tensors(config_from_dict(cfg), w, dtype=dtype, max_tokens=1024, max_slots=4, mark_freed_pages=True)
+    a, b, c = (random_tokens(n, cfg["vocab"], 7 * seed + n) for n in (75, 130, 9))
+    close(run_in_pieces(e, a, [len(a)]), P.forward(cfg, w, a).float(), dtype, f"seed {seed}: whole")
+    sb, sc = e.alloc_slot(), e.alloc_slot()
+    got_b = [e.step([StepEntry(sb, b[:66], list(range(66))), StepEntry(sc, c[:8], [])])[:66]]
+    got_b.append(e.step([StepEntry(sb, [b[66]], [0]), StepEntry(sc, [c[8]], [])]))
+    e.free_slot(sc)
+    for t in b[67:]:
+        got_b.append(e.step([StepEntry(sb, [t], [0])]))
+    e.free_slot(sb)
+    close(torch.cat(got_b).float().cpu(), P.forward(cfg, w, b).float(), dtype, f"seed {seed}: prompt in a batch, then single tokens")
+    e.check_kernels()
+    e.cache.check()

@@ -199,14 +199,15 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     if (!is_q && !is_k) {   // V: into the cache as it is, or blended with an earlier layer's values of the same token first
         const int vh = head - a.nh - a.nkv;
         TOut* dst = to_cache ? (TOut*)a.cache.storage + kv_half_elems(a.cache) + kv_row_offset(a.cache, slot, pos, vh) : nullptr;
-        const TOut* vf = a.v_first ? (const TOut*)a.v_first + (size_t)t * a.v_first_stride + vh * hd : nullptr;
+        const int vf_head = a.v_first_head > 0 ? a.v_first_head : hd;
+        const TOut* vf = a.v_first ? (const TOut*)a.v_first + (size_t)t * a.v_first_stride + vh * vf_head : nullptr;
         TOut* keep = a.v_keep ? (TOut*)a.v_keep + (size_t)t * a.v_keep_stride + vh * hd : nullptr;
         const float lam = vf ? *a.v_mix : 0.f;
 #pragma unroll
         for (int j = 0; j < QK_MAXE; ++j) {
             const int e = lane + 32 * j;
             if (e >= hd) continue;
-            const float val = vf ? (1.0f - lam) * v[j] + lam * ldf(vf + e) : v[j];
+            const float val = vf ? (1.0f - lam) * v[j] + lam * (e < vf_head ? ldf(vf + e) : 0.f) : v[j];
             if (keep) stf(keep + e, val);
             if (dst) stf(dst + e, val);
         }

@@ -42,9 +42,12 @@ struct QkArgs {
     // norm_after: the mean is taken over the rotated head (after the rotation) instead of before it.
     int norm_dims; int norm_after;
     // Values blended across layers: V head rows become (1 - *v_mix) v + *v_mix v_first[t] before they go anywhere
-    // (v_first: rows [T][v_first_stride] of the output dtype, the kv heads side by side; null: no blending).  v_keep
+    // (v_first: rows [T][v_first_stride] of the output dtype, the kv heads side by side, each v_first_head wide; null: no blending).  v_keep
     // (null: nowhere) receives the V rows as they go to the cache, [T][v_keep_stride] in the output dtype: the place a later
     // layer blends with, or the step's own V columns, which the prompt kernels read.
     const void* v_first; int v_first_stride; const float* v_mix;
     void* v_keep; int v_keep_stride;
+    // Width of a head in the rows of v_first (0: hd): the layer that kept them may pad its heads to another width than this
+    // one; elements beyond the narrower of the two are padding (zero) on both sides.
+    int v_first_head;
 };

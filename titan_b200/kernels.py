@@ -78,7 +78,8 @@ class QkArgs(Structure):
                 ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int), ("kv_len", c_void_p),
                 ("row_sumsq", c_void_p), ("row_parts", c_int), ("row_width", c_int), ("row_eps", c_float),
                 ("norm_dims", c_int), ("norm_after", c_int),
-                ("v_first", c_void_p), ("v_first_stride", c_int), ("v_mix", c_void_p), ("v_keep", c_void_p), ("v_keep_stride", c_int)]
+                ("v_first", c_void_p), ("v_first_stride", c_int), ("v_mix", c_void_p), ("v_keep", c_void_p), ("v_keep_stride", c_int),
+                ("v_first_head", c_int)]
 
 
 class AttnArgs(Structure):

@@ -271,9 +271,11 @@ class AttentionMixer(Mixer):
                 ctx.carried[("values_of", s.option("layer_index"))] = kept
             else:
                 kept = ctx.carried.get(("values_of", first))
-                if kept is None or kept.shape != (T, KV):
+                if kept is None or kept.shape[0] != T or kept.shape[1] % s.num_kv_heads:
                     raise RuntimeError(f"the values of layer {first} that this layer blends with were not kept in this step")
-                qa.v_first, qa.v_first_stride, qa.v_mix = kept.data_ptr(), KV, self.mix_factor.data_ptr()
+                # (that layer may pad its heads to another width: the kernel reads a head's first elements from either)
+                qa.v_first, qa.v_first_stride, qa.v_mix = kept.data_ptr(), kept.shape[1], self.mix_factor.data_ptr()
+                qa.v_first_head = kept.shape[1] // s.num_kv_heads
                 if not wide_sum:                               # the step's own V columns are what a prompt's attention reads
                     qa.v_keep, qa.v_keep_stride = qkv.data_ptr() + (Q + KV) * qkv.element_size(), width
         folds_head_norm = wide_sum and ctx.options.get("fold_head_norm", True) and not self.extended

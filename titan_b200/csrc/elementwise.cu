@@ -774,7 +774,9 @@ __global__ void __launch_bounds__(256) dyt_kernel(const float* __restrict__ x, c
     pdl_wait();
     const size_t r = blockIdx.x, src = rows ? (size_t)rows[r] : r;
     const float al = *alpha;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) stf(y + r * H + i, tanhf(al * x[src * H + i]) * w[i] + b[i]);
+    // gridDim.y blocks share a row (a step of few rows would otherwise leave one block to walk a whole row, load after load)
+    const int per = (H + gridDim.y - 1) / gridDim.y, i0 = blockIdx.y * per, i1 = min(H, i0 + per);
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) stf(y + r * H + i, tanhf(al * x[src * H + i]) * w[i] + b[i]);
 }
 
 template <typename T>
@@ -785,7 +787,8 @@ __global__ void __launch_bounds__(256) scale_add_kernel(float* __restrict__ y, c
     pdl_wait();
     const size_t r = blockIdx.x;
     const float al = h ? *alpha : 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const int per = (H + gridDim.y - 1) / gridDim.y, i0 = blockIdx.y * per, i1 = min(H, i0 + per);      // gridDim.y blocks share a row
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const size_t at = r * H + i;
         const float v = fmaf(y[at], s ? s[i] : 1.f, x[at]);
         x[at] = v;
@@ -794,11 +797,15 @@ __global__ void __launch_bounds__(256) scale_add_kernel(float* __restrict__ y, c
     }
 }
 
+// Blocks that share a row of H elements: one while the rows alone fill the machine, else one per 256 elements.
+static int row_parts(int n_rows, int H) { return n_rows >= 256 ? 1 : (H + 255) / 256; }
+
 extern "C" int tb_dyt(const float* x, const float* w, const float* b, const float* alpha, void* y, int dtype, const int* rows, int n_rows,
                       int H, cudaStream_t stream) {
     TB_REQUIRE(n_rows > 0 && H > 0 && x && w && b && alpha && y, "dyt: sizes must be positive and every tensor given");
-    if (dtype == TB_F32) tb_launch(dyt_kernel<float>, n_rows, 256, 0, stream, x, w, b, alpha, (float*)y, rows, H);
-    else if (dtype == TB_BF16) tb_launch(dyt_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, x, w, b, alpha, (__nv_bfloat16*)y, rows, H);
+    const dim3 grid(n_rows, row_parts(n_rows, H));
+    if (dtype == TB_F32) tb_launch(dyt_kernel<float>, grid, 256, 0, stream, x, w, b, alpha, (float*)y, rows, H);
+    else if (dtype == TB_BF16) tb_launch(dyt_kernel<__nv_bfloat16>, grid, 256, 0, stream, x, w, b, alpha, (__nv_bfloat16*)y, rows, H);
     else TB_REQUIRE(false, "dyt: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("dyt");
     return 0;
@@ -808,8 +815,9 @@ extern "C" int tb_scale_add(float* y, const float* s, float* x, int zero_y, cons
                             int dtype, int n_rows, int H, cudaStream_t stream) {
     TB_REQUIRE(n_rows > 0 && H > 0 && x && y, "scale_add: sizes must be positive");
     TB_REQUIRE(!h || (w && b && alpha), "scale_add: the norm of the new rows needs its weight, bias and factor");
-    if (dtype == TB_F32) tb_launch(scale_add_kernel<float>, n_rows, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (float*)h, H);
-    else if (dtype == TB_BF16) tb_launch(scale_add_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (__nv_bfloat16*)h, H);
+    const dim3 grid(n_rows, row_parts(n_rows, H));
+    if (dtype == TB_F32) tb_launch(scale_add_kernel<float>, grid, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (float*)h, H);
+    else if (dtype == TB_BF16) tb_launch(scale_add_kernel<__nv_bfloat16>, grid, 256, 0, stream, y, s, x, zero_y, w, b, alpha, (__nv_bfloat16*)h, H);
     else TB_REQUIRE(false, "scale_add: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("scale_add");
     return 0;

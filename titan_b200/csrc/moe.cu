@@ -353,7 +353,8 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const int per = (H + gridDim.y - 1) / gridDim.y, i0 = blockIdx.y * per, i1 = min(H, i0 + per);      // gridDim.y blocks share a row (steps of few rows)
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
             if (ids && ids[t * top + k] >= n_real) { s = fmaf(wts[t * top + k], ldf(x + t * ldx + i), s); continue; }
@@ -450,10 +451,11 @@ extern "C" int tb_moe_combine(const float* y, const float* wts, const float* sha
     TB_REQUIRE(T_ > 0 && H > 0 && top > 0 && y && wts && out, "moe_combine: sizes must be positive");
     TB_REQUIRE(!ids || (x && ldx >= H && n_real > 0), "moe_combine: experts without matrices need the tokens' input rows");
     const int threads = H >= 1024 ? 256 : 128;
+    const dim3 grid(T_, T_ >= 256 ? 1 : (H + threads - 1) / threads);
     if (ids && x_dtype == TB_BF16)
-        tb_launch(moe_combine_kernel<__nv_bfloat16>, T_, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const __nv_bfloat16*)x, ldx);
+        tb_launch(moe_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const __nv_bfloat16*)x, ldx);
     else
-        tb_launch(moe_combine_kernel<float>, T_, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const float*)x, ldx);
+        tb_launch(moe_combine_kernel<float>, grid, threads, 0, stream, y, wts, shared_y, gate, out, H, top, where, ids, n_real, (const float*)x, ldx);
     TB_CHECK_LAUNCH("moe_combine");
     return 0;
 }

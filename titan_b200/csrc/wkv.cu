@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(256) wkv_shift_kernel(WkvArgs a) {
     const T* before = cur - a.h_stride;
     const float* last = a.state + (size_t)a.slot_of_seq[seq] * a.state_stride + (size_t)a.H * a.dk * a.dk;
     T* out = (T*)a.mixes + (size_t)t * a.mix_stride;
-    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+    const int per = (a.W + gridDim.y - 1) / gridDim.y, i0 = blockIdx.y * per, i1 = min(a.W, i0 + per);      // gridDim.y blocks share a row
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const float x = ldf(cur + i), p = first ? last[i] : ldf(before + i);
 #pragma unroll
         for (int s = 0; s < 5; ++s) stf(out + (size_t)s * a.W + i, x + (p - x) * a.mu[(size_t)s * a.W + i]);
@@ -255,7 +256,7 @@ cudaError_t launch_scan(const WkvArgs& a, cudaStream_t stream) {
 
 template <typename T>
 int run(const WkvArgs& a, int stage, cudaStream_t stream) {
-    if (stage == 0) tb_launch(wkv_shift_kernel<T>, a.T, 256, 0, stream, a);
+    if (stage == 0) tb_launch(wkv_shift_kernel<T>, dim3(a.T, a.T >= 256 ? 1 : (a.W + 255) / 256), 256, 0, stream, a);      // few rows: a block per 256 elements
     else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3((a.T + DEC_TOK - 1) / DEC_TOK, (a.H * a.dk + 127) / 128), 128, 0, stream, a);
     else if (stage == 2) {
         // eight lanes a column while four would leave SMs without a block (148 on this chip), for heads up to 128 wide

@@ -42,7 +42,35 @@ struct WkvArgs {
 
 namespace {
 
-template <typename T>
+// Eight consecutive elements of a row as floats, from one (bfloat16) or two (float32) 16-byte accesses.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* o);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* o) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 q = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&q);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// VEC: rows, strides and pointers allow 16-byte accesses of eight elements (the launcher checks); else element by element.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) wkv_shift_kernel(WkvArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -52,11 +80,32 @@ __global__ void __launch_bounds__(256) wkv_shift_kernel(WkvArgs a) {
     const T* before = cur - a.h_stride;
     const float* last = a.state + (size_t)a.slot_of_seq[seq] * a.state_stride + (size_t)a.H * a.dk * a.dk;
     T* out = (T*)a.mixes + (size_t)t * a.mix_stride;
-    const int per = (a.W + gridDim.y - 1) / gridDim.y, i0 = blockIdx.y * per, i1 = min(a.W, i0 + per);      // gridDim.y blocks share a row
-    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-        const float x = ldf(cur + i), p = first ? last[i] : ldf(before + i);
+    constexpr int E = VEC ? 8 : 1;
+    const int units = a.W / E;                          // gridDim.y blocks share a row
+    const int per = (units + gridDim.y - 1) / gridDim.y, u0 = blockIdx.y * per, u1 = min(units, u0 + per);
+    for (int u = u0 + threadIdx.x; u < u1; u += blockDim.x) {
+        const int i = u * E;
+        float x[E], p[E];
+        if (VEC) {
+            load8<T>(cur + i, x);
+            if (first) {                                 // (the state's row is float32 and need not be 16-byte aligned)
 #pragma unroll
-        for (int s = 0; s < 5; ++s) stf(out + (size_t)s * a.W + i, x + (p - x) * a.mu[(size_t)s * a.W + i]);
+                for (int k = 0; k < E; ++k) p[k] = last[i + k];
+            } else load8<T>(before + i, p);
+        } else {
+            x[0] = ldf(cur + i);
+            p[0] = first ? last[i] : ldf(before + i);
+        }
+#pragma unroll
+        for (int s = 0; s < 5; ++s) {
+            float m[E], o[E];
+            if (VEC) load8<float>(a.mu + (size_t)s * a.W + i, m);
+            else m[0] = a.mu[(size_t)s * a.W + i];
+#pragma unroll
+            for (int k = 0; k < E; ++k) o[k] = x[k] + (p[k] - x[k]) * m[k];
+            if (VEC) store8<T>(out + (size_t)s * a.W + i, o);
+            else stf(out + (size_t)s * a.W + i, o[0]);
+        }
     }
 }
 
@@ -256,7 +305,14 @@ cudaError_t launch_scan(const WkvArgs& a, cudaStream_t stream) {
 
 template <typename T>
 int run(const WkvArgs& a, int stage, cudaStream_t stream) {
-    if (stage == 0) tb_launch(wkv_shift_kernel<T>, dim3(a.T, a.T >= 256 ? 1 : (a.W + 255) / 256), 256, 0, stream, a);      // few rows: a block per 256 elements
+    if (stage == 0) {
+        auto ok16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+        const bool vec = a.W % 8 == 0 && a.h_stride % 8 == 0 && a.mix_stride % 8 == 0 && ok16(a.h) && ok16(a.mixes) && ok16(a.mu);
+        const int units = vec ? a.W / 8 : a.W;
+        const dim3 grid(a.T, a.T >= 256 ? 1 : (units + 255) / 256);      // few rows: a block per 256 accesses of a row
+        if (vec) tb_launch(wkv_shift_kernel<T, true>, grid, 256, 0, stream, a);
+        else tb_launch(wkv_shift_kernel<T, false>, grid, 256, 0, stream, a);
+    }
     else if (stage == 1) tb_launch(wkv_decay_kernel<T>, dim3((a.T + DEC_TOK - 1) / DEC_TOK, (a.H * a.dk + 127) / 128), 128, 0, stream, a);
     else if (stage == 2) {
         // eight lanes a column while four would leave SMs without a block (148 on this chip), for heads up to 128 wide

@@ -436,8 +436,8 @@ def test_a_batch_of_unequal_requests_against_each_alone_and_slots_used_again(nam
     e = wd.engine(dtype)
     reqs = wd.requests
     tail = 6
-    for round_ in range(2):
-        order = list(range(len(reqs))) if round_ == 0 else list(reversed(range(len(reqs))))
+    for turn in range(2):
+        order = list(range(len(reqs))) if turn == 0 else list(reversed(range(len(reqs))))
         heads = {i: max(1, len(reqs[i]) - tail) for i in order}
         slots = {i: e.alloc_slot() for i in order}
         got = {i: [] for i in order}
@@ -454,9 +454,9 @@ def test_a_batch_of_unequal_requests_against_each_alone_and_slots_used_again(nam
                 got[i].append(out[k:k + 1].float().cpu())
                 at[i] += 1
                 if at[i] == len(reqs[i]):
-                    e.free_slot(slots[i])                      # a shorter request leaves; its slot may be taken in the next round
+                    e.free_slot(slots[i])                      # a shorter request leaves; its slot may be taken in the next turn
         for i in order:
-            close(torch.cat(got[i]), wd.plain(reqs[i]), dtype, f"{name}: request {i} in a batch, round {round_}")
+            close(torch.cat(got[i]), wd.plain(reqs[i]), dtype, f"{name}: request {i} in a batch, turn {turn}")
         e.cache.check()
     e.check_kernels()
 

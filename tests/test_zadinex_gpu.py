@@ -557,11 +557,15 @@ def test_trace_runner_as_a_subprocess(tmp_path):
         if i == 0:
             es.append({"id": "b", "tokens": [b[20]], "want": [0]})
         steps.append({"step": i + 1, "entries": es, "end": ["b"] if i == 0 else []})
+    # then many short requests at once: each holds a page of its own, far more pages than --max-tokens / 64
+    many = [random_tokens(3, cfg["vocab"], 30 + i) for i in range(20)]
+    steps.append({"step": 11, "entries": [{"id": f"m{i}", "tokens": m[:2], "want": []} for i, m in enumerate(many)], "end": []})
+    steps.append({"step": 12, "entries": [{"id": f"m{i}", "tokens": m[2:], "want": [0]} for i, m in enumerate(many)], "end": [f"m{i}" for i in range(20)]})
     out = tmp_path / "out"
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(out), "--max-tokens", "192"],
                        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
     assert p.returncode == 0, p.stderr[-2000:]
-    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(13)]
     cfg_full = make_config("odd")
     pa, pb = P.forward(cfg_full, weights, a).float(), P.forward(cfg_full, weights, b).float()
     V = cfg["vocab"]
@@ -571,6 +575,8 @@ def test_trace_runner_as_a_subprocess(tmp_path):
     rows_close(one, torch.stack([pa[60], pb[20]]), "float32", "step 1")
     last = torch.from_numpy(np.fromfile(out / "10.f32", dtype="<f4").reshape(-1, V))
     rows_close(last, pa[69:70], "float32", "step 10")
+    short = torch.from_numpy(np.fromfile(out / "12.f32", dtype="<f4").reshape(-1, V))
+    rows_close(short, torch.stack([P.forward(cfg_full, weights, m).float()[2] for m in many]), "float32", "twenty short requests")
 
 
 def test_command_line_with_random_weights(tmp_path):

@@ -30,15 +30,18 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time (padding to whole pages not counted)")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
 
     print("[titan_b200] loading the engine (kernels are compiled on the first call)", file=sys.stderr, flush=True)
     from .cache import PAGE_SIZE
     from .engine import Engine, StepEntry
-    # room for what the live requests hold, each rounded up to whole pages, and a few pages to spare
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 8 * PAGE_SIZE)
+    # Room for what the live requests hold.  ``--max-tokens`` counts tokens without padding, and every live request
+    # holds whole pages: up to a page more than its tokens.  How many requests will be live at once is not known here
+    # (at most one per token), so the cache gets a page to spare for each of up to 1,024 requests, and a few more.
+    spare_pages = 8 + min(max(1, args.max_tokens), 1024)
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, max_tokens=args.max_tokens + spare_pages * PAGE_SIZE)
     print(f"[titan_b200] ready: {engine.spec.architecture}, {args.dtype}, cache of {engine.cache.num_pages} pages",
           file=sys.stderr, flush=True)
     slots: Dict[str, int] = {}
